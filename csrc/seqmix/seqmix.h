@@ -1,0 +1,31 @@
+// Launchers of the sequence-mixer kernels (raw pointers; `bf` / `*_bf16` flags: 1 = bfloat16 activations, 0 = float).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace seqmix {
+
+void short_conv(const void* x, int in_bf16, long x_sb, long x_st, const float* w, const float* bias, void* state, const int* slots,
+                const int* lens, int B, int S, int C, int taps, int fresh, int residual, void* out, int out_bf16, cudaStream_t s);
+void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const float* w, int w_stride, float eps, const void* gate,
+              long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, cudaStream_t s);
+void latent_kv_store(const void* kv, int bf, long kv_sb, long kv_st, int B, int S, int C, int R, int dims, const float* nw, float eps,
+                     const float* inv_freq, const int* pos0, const int* lens, const int* slots, void* cache, int ring, void* rows,
+                     cudaStream_t s);
+void rope_q(void* q, int bf, long q_sn, long q_sh, int N, int S, int H, int dims, const float* inv_freq, const int* pos0, cudaStream_t s);
+void latent_window_attention(const void* qa, int bf, long qa_sn, long qa_sh, const void* qr, long qr_sn, long qr_sh, const void* keys,
+                             long key_sb, int ring, const int* key_index, const int* pos0, const int* lens, int B, int S, int H, int C,
+                             int R, int window, float scale, void* out, long out_sn, long out_sh, cudaStream_t s);
+bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
+              const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int S,
+              int H, int D, int V, float* out, cudaStream_t s);
+void rglru_scan(const void* u, int bf, const float* gr, const float* gi, int wb, const float* rbias, const float* ibias,
+                const float* lam_sp, const void* y, long y_sb, long y_st, float* state, const int* slots, const int* lens, int fresh,
+                int B, int S, int W, void* out, cudaStream_t s);
+void xielu(const void* x, void* out, int bf, long n, float ap, float an, cudaStream_t s);
+void gelu_erf(const void* x, void* out, int bf, long n, cudaStream_t s);
+void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int O, int I, int act, void* out,
+                  cudaStream_t s);
+void moe_combine(const void* rows, const int* src, const float* weight, const void* base, int bf, int N, int top, int C, void* out,
+                 cudaStream_t s);
+
+}  // namespace seqmix

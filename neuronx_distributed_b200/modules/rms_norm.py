@@ -58,3 +58,26 @@ class RMSNorm(nn.Module):
 
     def extra_repr(self) -> str:
         return f"{tuple(self.weight.shape)}, eps={self.variance_epsilon}"
+
+
+class ScalarRMSNorm(nn.Module):
+    """RMS norm whose gain is ONE number for all coordinates: ``x / sqrt(mean(x^2) + eps) * g``.  ``add_to(res, y)`` is the
+    residual form of a block that normalises the sublayer's OUTPUT: ``res += norm(y)`` with ``res`` a float stream (one kernel,
+    ``csrc/seqmix/norms.cu``)."""
+
+    def __init__(self, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones((), dtype=torch.float32, device=device), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, input: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        from ..ops import seqmix
+
+        x = input
+        return seqmix.rms_norm(x.reshape(-1, x.shape[-1]), self.weight.reshape(1), self.eps, None, out_dtype or x.dtype).view(x.shape)
+
+    def add_to(self, res: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        from ..ops import seqmix
+
+        seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight.reshape(1), self.eps)
+        return res

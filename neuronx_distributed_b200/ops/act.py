@@ -47,3 +47,18 @@ class _SwiGLU(torch.autograd.Function):
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """``gate_up[..., :I]`` is gate, ``gate_up[..., I:]`` is up."""
     return _SwiGLU.apply(gate_up)
+
+
+def xielu(x: torch.Tensor, alpha_pos: float, alpha_neg: float) -> torch.Tensor:
+    """xIELU with prepared positive coefficients: ``z > 0: alpha_pos z^2 + z/2``; ``z <= 0: alpha_neg (exp(z) - 1 - z) + z/2``
+    (``csrc/seqmix/activations.cu``)."""
+    from . import seqmix
+
+    return seqmix.xielu(x, alpha_pos, alpha_neg)
+
+
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    """Exact GELU ``0.5 z (1 + erf(z / sqrt 2))`` (``csrc/seqmix/activations.cu``)."""
+    from . import seqmix
+
+    return seqmix.gelu_erf(x)

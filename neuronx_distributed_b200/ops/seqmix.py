@@ -1,0 +1,287 @@
+"""Sequence-mixer ops: short causal convolutions with carried history, scalar / vector RMS norms (optionally accumulated into a
+float residual stream), latent sliding-window attention over a ring cache, gated linear recurrences (per-key-channel decay; real-gated
+LRU), xIELU / erf-GELU and the small-batch pieces of a routed feed-forward.
+
+CUDA tensors run the hand-written kernels of ``csrc/seqmix`` (extension ``nxd_b200_seq_C``, built in-tree on first use so that a
+fresh checkout compiles only these few files); CPU tensors run the plain PyTorch statements below, which define the semantics.
+Conventions: activations are ``[B, S, ...]`` right-padded batches with ``lens [B]`` (int32) real tokens per row; ``slots [B]``
+(int32) names each row's block in a state tensor; ``fresh`` means the rows start a sequence in this call (history / state = 0).
+Everything the kernels keep in float (statistics, scores, decays, states) is float here as well."""
+from __future__ import annotations
+
+import importlib.machinery
+import importlib.util
+import math
+import os
+import sys
+from pathlib import Path
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext
+
+EXT_NAME = "nxd_b200_seq_C"
+SEQ_BUILD_DIR = _ext.BUILD_DIR / "seqmix"
+CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
+_C = None
+
+
+def build(verbose: bool = False) -> Path:
+    """Compile ``csrc/seqmix`` for sm_100a into ``_build/seqmix`` (IEEE math: no fast-math, the float paths are exact-rounded)."""
+    from torch.utils import cpp_extension
+
+    SEQ_BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
+    srcs = sorted(str(p) for p in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
+    cpp_extension.load(name=EXT_NAME, sources=srcs, extra_cflags=["-O3", "-std=c++17"],
+                       extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+                                          "--expt-relaxed-constexpr"],
+                       extra_include_paths=[str(CSRC)], build_directory=str(SEQ_BUILD_DIR), verbose=verbose, is_python_module=True,
+                       with_cuda=True)
+    so = SEQ_BUILD_DIR / f"{EXT_NAME}.so"
+    assert so.exists(), f"build did not produce {so}"
+    return so
+
+
+def ext():
+    """The extension module; built on first use when absent (needs nvcc, no GPU)."""
+    global _C
+    if _C is None:
+        so = SEQ_BUILD_DIR / f"{EXT_NAME}.so"
+        if not so.exists():
+            build()
+        loader = importlib.machinery.ExtensionFileLoader(EXT_NAME, str(so))
+        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(EXT_NAME, loader))
+        loader.exec_module(mod)
+        sys.modules[EXT_NAME] = mod
+        _C = mod
+    return _C
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def _i32(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.int32 else t.to(torch.int32)
+
+
+# --------------------------------------------------------------------------------------------------------------- short convolution
+def short_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, slots: torch.Tensor,
+               lens: torch.Tensor, fresh: bool, residual: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x [B,S,C]``, ``w [C,taps]`` float, ``state [slots, taps-1, C]`` of x's dtype (updated in place) → ``[B,S,C]``:
+    ``out_t = (x_t if residual) + bias + sum_j w[:, j] * in_(t-taps+1+j)``; rows past ``lens`` give zeros."""
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().short_conv(x, w, bias, state, _i32(slots), _i32(lens), fresh, residual, out_dtype == torch.bfloat16)
+    B, S, C = x.shape
+    taps = w.shape[1]
+    hist = torch.zeros(B, taps - 1, C, dtype=x.dtype) if fresh else state[slots.long()]
+    full = torch.cat([hist, x], 1).float()                                            # [B, taps-1+S, C]
+    out = sum(w[:, j] * full[:, j:j + S] for j in range(taps))
+    if bias is not None:
+        out = out + bias
+    if residual:
+        out = out + x.float()
+    keep = torch.arange(S)[None, :] < lens[:, None]
+    out = torch.where(keep[..., None], out, torch.zeros_like(out))
+    if taps > 1:
+        idx = lens.long()[:, None] + torch.arange(taps - 1)[None, :]                   # last taps-1 inputs end at hist+len
+        state[slots.long()] = torch.cat([hist, x], 1).gather(1, idx[..., None].expand(B, taps - 1, C))
+    return out.to(out_dtype)
+
+
+# --------------------------------------------------------------------------------------------------------------------------- norms
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, gate: Optional[torch.Tensor] = None,
+             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Rows of ``x [rows, C]`` divided by their root mean square, times ``w`` (``[C]`` or one number), times ``silu(gate)``."""
+    out_dtype = out_dtype or x.dtype
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().rms_norm(x, w, eps, gate, out_dtype == torch.bfloat16)
+    xf = x.float()
+    y = xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w
+    if gate is not None:
+        y = y * F.silu(gate.float())
+    return y.to(out_dtype)
+
+
+def add_rms_norm_(res: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """``res`` (float ``[rows, C]``) ``+= y / rms(y) * w`` in place."""
+    if _cuda(y):
+        _ext.count_launch()
+        ext().add_rms_norm_(res, y, w, eps)
+        return res
+    yf = y.float()
+    res += yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * w
+    return res
+
+
+# ---------------------------------------------------------------------------------------------------------------- latent attention
+def rotary_inv_freq(dims: int, base: float, device=None) -> torch.Tensor:
+    """``base^(-2i/dims)`` for i < dims/2, rounded once from float64."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).float().to(device)
+
+
+def _rotate(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, dims: int) -> torch.Tensor:
+    """x ``[..., n]`` float, pos broadcastable to x's leading dims: rotate-half on the first ``dims`` coordinates."""
+    half = dims // 2
+    ang = pos.float()[..., None] * inv_freq
+    c, s = torch.cos(ang), torch.sin(ang)
+    u, v = x[..., :half], x[..., half:dims]
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], -1)
+
+
+def latent_kv_store(kv: torch.Tensor, nw: torch.Tensor, eps: float, inv_freq: torch.Tensor, dims: int, pos0: torch.Tensor,
+                    lens: torch.Tensor, slots: torch.Tensor, cache: Optional[torch.Tensor], want_rows: bool) -> Optional[torch.Tensor]:
+    """``kv [B,S,C+R]``: RMS-norm (weight ``nw [C]``) of the first C numbers, rotation of the next ``dims`` at positions
+    ``pos0[b] + t``.  The last ``ring`` real tokens of each row go to ``cache [slots, ring, C+R]`` at row ``position mod ring``;
+    with ``want_rows`` the prepared rows come back as ``[B,S,C+R]``."""
+    if _cuda(kv):
+        _ext.count_launch()
+        rows = ext().latent_kv_store(kv, nw, eps, inv_freq, dims, _i32(pos0), _i32(lens), _i32(slots), cache, want_rows)
+        return rows if want_rows else None
+    B, S, _ = kv.shape
+    C = nw.numel()
+    f = kv.float()
+    c = f[..., :C]
+    c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * nw
+    pos = pos0.long()[:, None] + torch.arange(S)[None, :]
+    rows = torch.cat([c, _rotate(f[..., C:], pos, inv_freq, dims)], -1).to(kv.dtype)
+    if cache is not None:
+        ring = cache.shape[1]
+        for b in range(B):
+            n = int(lens[b])
+            for t in range(max(0, n - ring), n):
+                cache[int(slots[b]), int(pos[b, t]) % ring] = rows[b, t]
+    return rows if want_rows else None
+
+
+def rope_q_(q: torch.Tensor, off: int, dims: int, inv_freq: torch.Tensor, pos0: torch.Tensor) -> torch.Tensor:
+    """``q [B,S,H,Dq]``: coordinates ``[off, off+dims)`` of every head rotated in place at positions ``pos0[b] + t``."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().rope_q_(q, off, dims, inv_freq, _i32(pos0))
+        return q
+    S = q.shape[1]
+    pos = (pos0.long()[:, None] + torch.arange(S)[None, :])[:, :, None]
+    q[..., off:off + dims] = _rotate(q[..., off:off + dims].float(), pos, inv_freq, dims).to(q.dtype)
+    return q
+
+
+def latent_window_attention(qa: torch.Tensor, q: torch.Tensor, off: int, keys: torch.Tensor, key_index: Optional[torch.Tensor],
+                            pos0: torch.Tensor, lens: torch.Tensor, window: int, scale: float) -> torch.Tensor:
+    """``qa [H, B*S, C]`` absorbed queries, ``q [B,S,H,Dq]`` whose coordinates from ``off`` are the rotated part, ``keys
+    [blocks, ring, C+R]`` (row ``j mod ring`` of block ``key_index[b]``, or of block b, holds position j).  Position p sees
+    ``p - window < j <= p``.  Returns the attention-weighted sum of the latents ``[H, B*S, C]``; padded rows give zeros."""
+    if _cuda(qa):
+        _ext.count_launch()
+        return ext().latent_window_attention(qa, q, off, keys, None if key_index is None else _i32(key_index), _i32(pos0), _i32(lens),
+                                             window, scale)
+    H, N, C = qa.shape
+    B, S = q.shape[:2]
+    ring, R = keys.shape[1], keys.shape[2] - C
+    kb = keys[key_index.long()] if key_index is not None else keys                                  # [B, ring, C+R]
+    qq = torch.cat([qa.float().view(H, B, S, C).permute(1, 2, 0, 3), q[..., off:off + R].float()], -1)  # [B,S,H,C+R]
+    sc = torch.einsum("bshc,brc->bshr", qq, kb.float()) * scale
+    p = pos0.long()[:, None] + torch.arange(S)[None, :]                                              # [B,S]
+    r = torch.arange(ring)
+    j = p[..., None] - torch.remainder(p[..., None] - r, ring)                                       # position held by ring row r
+    ok = (j >= 0) & (j > p[..., None] - window)
+    sc = sc.masked_fill(~ok[:, :, None, :], float("-inf"))
+    o = torch.einsum("bshr,brc->bshc", torch.softmax(sc, -1), kb.float()[..., :C])
+    o = torch.where((torch.arange(S)[None, :] < lens[:, None])[..., None, None], o, torch.zeros_like(o))
+    return o.permute(2, 0, 1, 3).reshape(H, N, C).to(qa.dtype)
+
+
+# -------------------------------------------------------------------------------------------------------------------- recurrences
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, zbias: torch.Tensor, tau: float, state: torch.Tensor,
+             slots: torch.Tensor, lens: torch.Tensor, fresh: bool) -> torch.Tensor:
+    """``q, k [B,S,H,D]``, ``v [B,S,H,V]``, decay logits ``z [B,S,H*D]`` (+ ``zbias``) → float ``[B,S,H,V]``:
+    ``alpha = sigmoid(z)^(1/tau)``; ``S_t = diag(alpha_t) S_(t-1) + k_t v_t^T``; ``o_t = S_t^T q_t / sqrt(D)``.  ``state
+    [slots,H,D,V]`` float is read (unless ``fresh``) and left at each row's last real token."""
+    if _cuda(q):
+        _ext.count_launch()
+        return ext().gla_scan(q, k, v, z, zbias, tau, state, _i32(slots), _i32(lens), fresh)
+    B, S, H, D = q.shape
+    V = v.shape[-1]
+    alpha = torch.exp(F.logsigmoid(z.float() + zbias) / tau).view(B, S, H, D)
+    qf, kf, vf = q.float() * D ** -0.5, k.float(), v.float()
+    st = torch.zeros(B, H, D, V) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, H, V)
+    for t in range(S):
+        live = (t < lens)[:, None, None, None]
+        new = alpha[:, t, :, :, None] * st + kf[:, t, :, :, None] * vf[:, t, :, None, :]
+        st = torch.where(live, new, st)
+        out[:, t] = torch.where(live[..., 0], torch.einsum("bhdv,bhd->bhv", st, qf[:, t]), out[:, t])
+    state[slots.long()] = st
+    return out
+
+
+def rglru_scan(u: torch.Tensor, gr: torch.Tensor, gi: torch.Tensor, rbias: torch.Tensor, ibias: torch.Tensor, lam_sp: torch.Tensor,
+               y: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor, fresh: bool) -> torch.Tensor:
+    """``u [B,S,W]``; gate pre-activations ``gr, gi`` float ``[blocks, B*S, W/blocks]``; ``y [B,S,W]`` (pre-activation of the
+    gelu branch) → ``[B,S,W]``: ``a = exp(-8 sigmoid(gr + rbias) lam_sp)``, ``h_t = a h_(t-1) + sqrt(1 - a^2) sigmoid(gi + ibias)
+    u_t``, ``out = h_t * gelu_tanh(y_t)``.  ``state [slots, W]`` float."""
+    if _cuda(u):
+        _ext.count_launch()
+        return ext().rglru_scan(u, gr, gi, rbias, ibias, lam_sp, y, state, _i32(slots), _i32(lens), fresh)
+    B, S, W = u.shape
+    nb, _, wb = gr.shape
+    r = torch.sigmoid(gr.view(nb, B, S, wb).permute(1, 2, 0, 3).reshape(B, S, W) + rbias)
+    g = torch.sigmoid(gi.view(nb, B, S, wb).permute(1, 2, 0, 3).reshape(B, S, W) + ibias)
+    la = -8.0 * r * lam_sp
+    a, mult = torch.exp(la), torch.sqrt(-torch.expm1(2.0 * la))
+    h = torch.zeros(B, W) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, W)
+    for t in range(S):
+        live = (t < lens)[:, None]
+        h = torch.where(live, a[:, t] * h + mult[:, t] * g[:, t] * u[:, t].float(), h)
+        out[:, t] = torch.where(live, h * F.gelu(y[:, t].float(), approximate="tanh"), out[:, t])
+    state[slots.long()] = h
+    return out.to(u.dtype)
+
+
+# -------------------------------------------------------------------------------------------------- activations, routed small batch
+def xielu(x: torch.Tensor, ap: float, an: float) -> torch.Tensor:
+    """``z > 0: ap z^2 + z/2``; ``z <= 0: an (exp(z) - 1 - z) + z/2``."""
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().xielu(x.contiguous(), ap, an)
+    z = x.float()
+    return torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(z) - z) + 0.5 * z).to(x.dtype)
+
+
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().gelu_erf(x.contiguous())
+    return F.gelu(x.float()).to(x.dtype)
+
+
+def indexed_gemv(w: torch.Tensor, sel: torch.Tensor, x: torch.Tensor, gelu: bool) -> torch.Tensor:
+    """``w [E,O,I]``, ``sel [M]``, ``x [M,I]`` → ``act(w[sel[m]] @ x[m]) [M,O]`` (float accumulation)."""
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().indexed_gemv(w, _i32(sel), x, gelu)
+    y = torch.einsum("moi,mi->mo", w[sel.long()].float(), x.float())
+    return (F.gelu(y) if gelu else y).to(x.dtype)
+
+
+def moe_combine(rows: torch.Tensor, src: torch.Tensor, weight: torch.Tensor, base: Optional[torch.Tensor]) -> torch.Tensor:
+    """``out[n] = base[n] + sum_k weight[n,k] * rows[src[n,k]]`` summed in float; ``rows [M,C]``, ``src, weight [N,top]``."""
+    if _cuda(rows):
+        _ext.count_launch()
+        return ext().moe_combine(rows, _i32(src), weight, base)
+    y = (rows.float()[src.long()] * weight[..., None]).sum(1)
+    if base is not None:
+        y = y + base.float()
+    return y.to(rows.dtype)
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv))
