@@ -35,7 +35,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
         const long tok = (long)b * sb + (long)t * st;
         if (e < D) {
             float zz = ldf(z + (long)b * z_sb + (long)t * z_st + hq + e) + zbias[hq + e];
-            return expf(log_sigmoidf_(zz) * inv_tau);
+            return 1.f + expm1f(log_sigmoidf_(zz) * inv_tau);   // rounds once from an accurate value: no bias as alpha -> 1
         }
         if (e < 2 * D) return ldf(k + tok + hq + e - D);
         if (e < 3 * D) return ldf(q + tok + hq + e - 2 * D) * qscale;
@@ -136,7 +136,7 @@ __global__ void rglru_scan_kernel(const T* __restrict__ u, const float* __restri
     for (int t = 0; t < len; ++t) {
         const float r = sigmoidf_(gr[gbase + (long)t * wb] + rb), g = sigmoidf_(gi[gbase + (long)t * wb] + ib);
         const float uu = ldf(u + ((long)b * S + t) * W + c), yy = ldf(y + (long)b * y_sb + (long)t * y_st + c);
-        const float la = -8.f * r * sp, a = expf(la), mult = sqrtf(-expm1f(2.f * la));
+        const float la = -8.f * r * sp, a = 1.f + expm1f(la), mult = sqrtf(-expm1f(2.f * la));
         h = fmaf(a, h, mult * g * uu);
         const float gl = 0.5f * yy * (1.f + tanhf(0.7978845608028654f * (yy + 0.044715f * yy * yy * yy)));
         stf(out + ((long)b * S + t) * W + c, h * gl);
