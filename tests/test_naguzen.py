@@ -135,3 +135,350 @@ def close(got, want, tol):
 MIXED = [gla_spec(mlp=moe()), attn_spec(mlp=DENSE), lru_spec(mlp=moe(experts=4, top=1, shared=0)), attn_spec(window=5, heads=2, mlp=None),
          gla_spec(heads=1, dim=8, vdim=24, tau=2.0, mlp=DENSE)]
 TOL32 = 2e-4
+
+
+# ------------------------------------------------------------------------------------------------------------ single mechanisms
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("taps,residual,bias", [(1, True, False), (3, True, False), (4, False, True), (6, False, False)])
+def test_short_conv_prompt_then_tokens(device, taps, residual, bias):
+    g = torch.Generator().manual_seed(taps)
+    B, S, C, extra = 3, 9, 40, 5
+    lens = [9, 1, 4]
+    x = torch.randn(B, S + extra, C, generator=g)
+    w, b = torch.randn(C, taps, generator=g), (torch.randn(C, generator=g) if bias else None)
+    state = torch.full((5, taps - 1, C), 7.0)                                   # stale contents must be ignored by a fresh call
+    slots = torch.tensor([4, 0, 2], dtype=torch.int32)
+    dv = lambda t: None if t is None else t.to(device)
+    st = state.to(device)
+    out = seqmix.short_conv(dv(x[:, :S].contiguous()), dv(w), dv(b), st, dv(slots), dv(torch.tensor(lens, dtype=torch.int32)), True,
+                            residual, torch.float32).cpu()
+    got = [[out[i, t] for t in range(lens[i])] for i in range(B)]
+    for k in range(extra):                                                      # continue every row by single tokens
+        step = torch.stack([x[i, lens[i] + k] for i in range(B)])[:, None]
+        o = seqmix.short_conv(dv(step.contiguous()), dv(w), dv(b), st, dv(slots), dv(torch.ones(B, dtype=torch.int32)), False, residual,
+                              torch.float32).cpu()
+        for i in range(B):
+            got[i].append(o[i, 0])
+    for i in range(B):
+        seq = x[i, : lens[i] + extra].double()
+        want = oracle.short_conv(seq, w.double()) + (b.double() if bias else 0) + (seq if residual else 0)
+        assert torch.allclose(torch.stack(got[i]).double(), want, atol=1e-5), (i, taps)
+    assert (out[1, 1:] == 0).all() and (out[2, 4:] == 0).all()                  # padding rows are zeros
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_norms_and_activations(device):
+    g = torch.Generator().manual_seed(1)
+    x, gate, res = torch.randn(11, 70, generator=g) * 3, torch.randn(11, 70, generator=g), torch.randn(11, 70, generator=g)
+    w, one = torch.rand(70, generator=g) + 0.5, torch.tensor([0.37])
+    eps = 1e-3
+    dv = lambda t: t.to(device)
+    want = oracle.rms(x.double(), eps)
+    assert torch.allclose(seqmix.rms_norm(dv(x), dv(w), eps).cpu().double(), want * w, atol=1e-5)
+    assert torch.allclose(seqmix.rms_norm(dv(x), dv(one), eps).cpu().double(), want * 0.37, atol=1e-5)
+    gated = seqmix.rms_norm(dv(x), dv(w), eps, gate=dv(gate)).cpu().double()
+    assert torch.allclose(gated, want * w * (gate * torch.sigmoid(gate)).double(), atol=1e-5)
+    wide = torch.randn(11, 90, generator=g)                                     # a norm over the first columns of wider rows
+    assert torch.allclose(seqmix.rms_norm(dv(wide)[:, :70], dv(w), eps).cpu().double(), oracle.rms(wide[:, :70].double(), eps) * w, atol=1e-5)
+    r = dv(res.clone())
+    seqmix.add_rms_norm_(r, dv(x), dv(one), eps)
+    assert torch.allclose(r.cpu().double(), res.double() + want * 0.37, atol=1e-5)
+    z = torch.cat([torch.randn(500, generator=g) * 3, torch.tensor([0.0, -30.0, 1e-4, -1e-4])])
+    act = torch.tensor([0.3, -0.4])
+    sp = torch.nn.functional.softplus(act)
+    assert torch.allclose(seqmix.xielu(dv(z), float(sp[0]), float(0.5 + sp[1])).cpu().double(), oracle.xielu(z.double(), act.double()), atol=1e-5)
+    assert torch.allclose(seqmix.gelu_erf(dv(z)).cpu().double(), oracle.gelu_erf(z.double()), atol=1e-5)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("rows,top,shared", [(5, 3, 40), (70, 3, 40), (40, 1, 0), (9, 2, 0)])
+def test_routed_ffn(device, rows, top, shared):
+    f = moe(experts=6, top=top, scale=1.7, ff=24, shared=shared)
+    cfg = make_cfg([gla_spec(mlp=f)])
+    w = random_checkpoint(cfg, seed=rows)
+    P = oracle.sub(w, "l0.mlp.")
+    m = RoutedFFN(cfg["width"], 24, 6, top, weight_scale=1.7, shared_ff=shared, dtype=torch.float32, device=device)
+    with torch.no_grad():
+        m.up.copy_(torch.stack([P[f"e{e}.up"] for e in range(6)]))
+        m.down.copy_(torch.stack([P[f"e{e}.down"] for e in range(6)]))
+        m.router.linear_router.weight.copy_(P["router"])
+        if shared:
+            m.shared_up.copy_(P["shared.up"]), m.shared_down.copy_(P["shared.down"])
+    h = torch.randn(rows, cfg["width"], generator=torch.Generator().manual_seed(3))
+    want = oracle.moe_ff(h.double(), {k: v.double() for k, v in P.items()}, f)
+    assert torch.allclose(m(h.to(device)).cpu().double(), want, atol=2e-5)
+
+
+SINGLE = {"attention": [attn_spec()], "attention_wide_window": [attn_spec(window=64, heads=1, dim=8, rot=4, vdim=8, kv_rank=100, q_rank=16)],
+          "gla": [gla_spec()], "gla_one_head": [gla_spec(heads=1, dim=40, vdim=72, tau=1.0)], "rglru": [lru_spec()],
+          "rglru_one_block": [lru_spec(width=40, blocks=1, conv=1)], "dense": [gla_spec(mlp=DENSE)], "moe": [lru_spec(mlp=moe())]}
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_single_layer_models(device, name):
+    """One layer of each kind: the whole prompt at once, and one token followed by token-by-token decoding, against the oracle."""
+    cfg = make_cfg(SINGLE[name], taps=2 if "one" in name else 3)
+    w = random_checkpoint(cfg, seed=len(name))
+    toks = tokens_for(cfg, 26, 5)
+    want, _ = oracle.forward(complete_config(cfg, {k: v.shape for k, v in w.items()}), w, toks)
+    model = build(cfg, w, device)
+    close(run_alone(model, toks, len(toks)), want, TOL32)
+    close(run_alone(model, toks, 1), want, TOL32)
+
+
+# ------------------------------------------------------------------------------------------------------------------ whole models
+@pytest.fixture(scope="module")
+def mixed():
+    cfg = make_cfg(MIXED)
+    w = random_checkpoint(cfg, seed=11)
+    toks = tokens_for(cfg, 48, 7)
+    want, trail = oracle.forward(complete_config(cfg, {k: v.shape for k, v in w.items()}), w, toks)
+    return cfg, w, toks, want, trail
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("prompt", [48, 1, 2, 6, 31])
+def test_prompt_then_decode_matches_oracle(device, mixed, prompt):
+    """Windows of 7 and 5 pass several times over decoded tokens; the first tokens (position < taps, < window) are covered by prompt 1, 2."""
+    cfg, w, toks, want, _ = mixed
+    close(run_alone(build(cfg, w, device), toks, prompt), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_residual_stream_after_every_layer(device, mixed):
+    cfg, w, toks, _, trail = mixed
+    model = build(cfg, w, device)
+    seen = []
+    model.forward_step(torch.tensor([toks], device=device), [len(toks)], [model.states.alloc()], [0], True, tap=lambda i, x: seen.append(x[0].cpu().clone()))
+    for i, (a, b) in enumerate(zip(seen, trail)):
+        assert torch.allclose(a.double(), b, atol=2e-4, rtol=1e-4), f"layer {i}"
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_unequal_batch_against_each_alone_and_reused_slots(device, mixed):
+    cfg, w, toks, _, _ = mixed
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    model = build(cfg, w, device)
+    reqs = [tokens_for(cfg, n, 20 + n) for n in (1 + 6, 7 + 6, 23 + 6, 2 + 6)]
+    prompts, steps = [1, 7, 23, 2], [0, 6, 3, 6]                      # row 0 ends with its prompt, row 2 leaves early
+    mgr = model.states
+    warm = [mgr.alloc() for _ in range(3)]                            # dirty a few slots first, then give them back
+    model.forward_step(torch.randint(0, 50, (3, 9), device=device), [9, 9, 9], warm, [0, 0, 0], True)
+    for s in warm:
+        mgr.free(s)
+    slots = [mgr.alloc() for _ in reqs]
+    assert set(warm) <= set(slots)
+    S = max(prompts)
+    ids = torch.zeros(len(reqs), S, dtype=torch.long)
+    for b, (r, p) in enumerate(zip(reqs, prompts)):
+        ids[b, :p] = torch.tensor(r[:p])
+    x = model.forward_step(ids.to(device), prompts, slots, [0] * len(reqs), True)
+    got = [[model.logits(x[b, :p]).cpu()] for b, p in enumerate(prompts)]
+    live = [b for b in range(len(reqs)) if steps[b] > 0]
+    mgr.free(slots[0])
+    for k in range(max(steps)):
+        live = [b for b in live if k < steps[b]]
+        step_ids = torch.tensor([[reqs[b][prompts[b] + k]] for b in live], device=device)
+        x = model.forward_step(step_ids, [1] * len(live), [slots[b] for b in live], [prompts[b] + k for b in live], False)
+        lg = model.logits(x[:, 0]).cpu()
+        for j, b in enumerate(live):
+            got[b].append(lg[j:j + 1])
+    for b, r in enumerate(reqs):
+        n = prompts[b] + steps[b]
+        want, _ = oracle.forward(full, w, r[:n])
+        close(torch.cat(got[b]), want, TOL32)
+    fresh = build(cfg, w, device)
+    close(torch.cat(got[2]), run_alone(fresh, reqs[2][:26], 23), 1e-5)      # the batch changes nothing beyond rounding
+
+
+def test_state_manager_slots():
+    mgr = SequenceStateManager([{"a": ((2, 3), torch.float32)}, {"b": ((4,), torch.bfloat16)}], num_slots=2)
+    s = [mgr.alloc() for _ in range(5)]                                 # grows past the first allocation, keeping contents
+    assert sorted(s) == [0, 1, 2, 3, 4] and mgr.layer(0)["a"].shape[0] >= 5 and mgr.layer(1)["b"].dtype == torch.bfloat16
+    mgr.layer(0)["a"][3] = 5.0
+    mgr.free(1), mgr.free(3)
+    assert mgr.alloc() == 1 and mgr.alloc() == 3 and mgr.in_use == 5
+    assert float(mgr.layer(0)["a"][3].sum()) == 30.0                    # a reused slot is handed out as it was left
+    mgr.advance([1, 3], [4, 1])
+    assert mgr.length[1] == 4 and mgr.length[3] == 1
+    with pytest.raises(KeyError):
+        mgr.free(7)
+
+
+# ------------------------------------------------------------------------------------------------- edges, far keys, long decoding
+def _needle_model(layers, vocab=40, width=48, seed=3):
+    """Token 0 is the needle: its embedding is large, so wherever a layer can still see it the logits move by a lot."""
+    cfg = make_cfg(layers, vocab=vocab, width=width)
+    w = random_checkpoint(cfg, seed=seed)
+    w["embed"][0] = (w["embed"][0] * 12).to(torch.bfloat16).float()
+    return cfg, w
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("prompt", [40, 12, 1])
+def test_window_edges_with_a_needle(device, prompt):
+    """The needle sits at position 9 of an attention-only model with window 6 (taps 1 → no other path to the past): positions 9..14
+    see it, 15 on do not.  Checked in a prompt, and with the edge passing over decoded tokens."""
+    window, at = 6, 9
+    cfg, w = _needle_model([attn_spec(window=window, heads=2), attn_spec(window=window, heads=2, dim=8, rot=8, vdim=16, kv_rank=24, q_rank=16)])
+    cfg["canon"]["taps"] = 1
+    for k in [k for k in w if "canon" in k]:
+        w[k] = w[k][:, :1]
+    toks = [1 + t % 7 for t in range(40)]
+    plain = list(toks)
+    toks[at] = 0
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    want, _ = oracle.forward(full, w, toks)
+    base, _ = oracle.forward(full, w, plain)
+    moved = (want - base).abs().amax(-1)
+    reach = at + 2 * (window - 1)                                      # two layers: the needle's trace travels two windows
+    assert (moved[at:at + window] > 1e-2).all() and (moved[reach + 1:] < 1e-9).all() and (moved[:at] < 1e-9).all()
+    assert moved[reach] > 1e-6
+    close(run_alone(build(cfg, w, device), toks, prompt), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("layer", ["gla", "rglru"])
+def test_far_key_through_a_recurrent_state(device, layer):
+    """A needle 300 tokens back is still in the state: slow decays, a long prompt, then decoding; a lost or restarted state shows."""
+    spec = gla_spec(heads=2, dim=16, vdim=16, tau=64.0) if layer == "gla" else lru_spec(width=64, blocks=2, conv=2)
+    cfg, w = _needle_model([spec], seed=5)
+    if layer == "rglru":
+        w["l0.mix.lam"] = torch.full_like(w["l0.mix.lam"], -7.0)            # a close to 1: long memory
+    else:
+        w["l0.mix.a2.b"] = torch.full_like(w["l0.mix.a2.b"], 5.0)
+    toks = [1 + (t * 5) % 11 for t in range(330)]
+    plain = list(toks)
+    toks[4] = 0
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    want, _ = oracle.forward(full, w, toks)
+    base, _ = oracle.forward(full, w, plain)
+    assert (want[-1] - base[-1]).abs().max() > 1e-3                         # the far token still matters at the end
+    model = build(cfg, w, device)
+    close(run_alone(model, toks, 300), want, TOL32)
+    close(run_alone(model, toks, 330), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_long_decoding_from_one_token(device):
+    cfg = make_cfg([attn_spec(window=16, mlp=moe(top=2)), gla_spec(mlp=DENSE), lru_spec(mlp=None)], taps=4)
+    w = random_checkpoint(cfg, seed=21)
+    toks = tokens_for(cfg, 150, 9)
+    want, _ = oracle.forward(complete_config(cfg, {k: v.shape for k, v in w.items()}), w, toks)
+    close(run_alone(build(cfg, w, device), toks, 1), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_window_larger_than_the_cache_limit(device):
+    """A window wider than the serving length: the ring is cut to the serving length and nothing wraps."""
+    cfg = make_cfg([attn_spec(window=1000)])
+    w = random_checkpoint(cfg, seed=2)
+    toks = tokens_for(cfg, 30, 1)
+    want, _ = oracle.forward(cfg, w, toks)
+    model = build(cfg, w, device, max_seq_len=32)
+    assert model.states.layer(0)["kv"].shape[1] == 32
+    close(run_alone(model, toks, 11), want, TOL32)
+
+
+# ---------------------------------------------------------------------------------------------- entry points, registry, runner
+def _oracle_greedy(full, w, prompt, n):
+    seq = list(prompt)
+    for _ in range(n):
+        logits, _ = oracle.forward(full, w, seq)
+        seq.append(int(logits[-1].argmax()))
+    return seq[len(prompt):]
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_greedy_generation_through_the_serving_entry_points(device, mixed):
+    cfg, w, _, _, _ = mixed
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    prompts = [tokens_for(cfg, 9, 1), tokens_for(cfg, 4, 2)]
+    want = [_oracle_greedy(full, w, p, 6) for p in prompts]
+    model = build(cfg, w, device, batch_size=2)
+    model.on_device_sampling = True
+    ids = torch.zeros(2, 9, dtype=torch.long)
+    mask = torch.zeros(2, 9, dtype=torch.long)
+    for b, p in enumerate(prompts):
+        ids[b, :len(p)], mask[b, :len(p)] = torch.tensor(p), 1
+    got = model.generate(ids.to(device), 6, prompt_lens=torch.tensor([9, 4], device=device))
+    assert got.cpu().tolist() == want
+    out = HuggingFaceGenerationAdapter(model, pad_token_id=0).generate(ids.to(device), attention_mask=mask.to(device), max_new_tokens=6)
+    assert out[:, 9:].cpu().tolist() == want
+    again = model.generate(ids.to(device), 6, prompt_lens=torch.tensor([9, 4], device=device))      # same slots, used again
+    assert again.cpu().tolist() == want
+
+
+def _save_model_dir(path, cfg, w):
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    ints = {}
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
+def _trace(cfg):
+    a, b, c = tokens_for(cfg, 12, 31), tokens_for(cfg, 5, 32), tokens_for(cfg, 1, 33)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:9], "want": [0, 8]}, {"id": "c", "tokens": c, "want": [0]},
+                                     {"id": "b", "tokens": b[:3], "want": []}], "end": ["c"]}]
+    for k in range(3):
+        e = [{"id": "a", "tokens": [a[9 + k]], "want": [0]}]
+        if k < 2:
+            e.append({"id": "b", "tokens": [b[3 + k]], "want": [0] if k else []})
+        steps.append({"step": k + 1, "entries": e, "end": ["b"] if k == 1 else (["a"] if k == 2 else [])})
+    steps.append({"step": 4, "entries": [{"id": "d", "tokens": b, "want": [4]}], "end": ["d"]})        # a freed slot, used again
+    rows = {0: [("a", 0), ("a", 8), ("c", 0)], 1: [("a", 9)], 2: [("a", 10), ("b", 4)], 3: [("a", 11)], 4: [("b", 4)]}
+    return {"a": a, "b": b, "c": c}, steps, rows
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_registry_checkpoint_reader_and_trace_replay(device, mixed, tmp_path):
+    import numpy as np
+
+    cfg, w, _, _, _ = mixed
+    path = _save_model_dir(str(tmp_path / "model"), cfg, w)
+    assert registry.family_of(cfg) == "naguzen" and "llama" in registry.families()
+    model = registry.load_for_serving(path, dtype=torch.float32, device=torch.device(device), max_seq_len=64, on_device_sampling=False)
+    assert isinstance(model, NaguzenForInference)
+    reqs, steps, rows = _trace(cfg)
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    want = {k: oracle.forward(full, w, v)[0] for k, v in reqs.items()}
+    out = tmp_path / "out"
+    out.mkdir()
+    rep = TraceReplayer(model, str(out))
+    for s in steps:
+        rep.step(s)
+    assert model.states.in_use == 0
+    for n, wanted in rows.items():
+        got = torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(wanted), cfg["vocab"]))
+        close(got, torch.stack([want[i][p] for i, p in wanted]), TOL32)
+
+
+def test_trace_runner_command_line(mixed, tmp_path):
+    import numpy as np
+
+    cfg, w, _, _, _ = mixed
+    path = _save_model_dir(str(tmp_path / "model"), cfg, w)
+    reqs, steps, rows = _trace(cfg)
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", path, "--dtype", "float32", "--out", str(out), "--max-tokens", "40"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600,
+                       env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {n}" for n in range(5)]
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    got = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, cfg["vocab"]))
+    close(got, torch.stack([oracle.forward(full, w, reqs["a"])[0][10], oracle.forward(full, w, reqs["b"])[0][4]]), TOL32)
+
+
+@pytest.mark.gpu
+def test_bfloat16_serving_close_to_the_oracle(mixed):
+    """The serving precision: bfloat16 matrix products, float statistics / states / residual.  Prompt + decode, against float64."""
+    cfg, w, toks, want, _ = mixed
+    model = build(cfg, w, "cuda", dtype=torch.bfloat16)
+    close(run_alone(model, toks, 20), want, 6e-2)
+    close(run_alone(model, toks, 48), want, 6e-2)
