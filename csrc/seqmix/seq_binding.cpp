@@ -125,9 +125,10 @@ Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
     TORCH_CHECK(q.is_cuda() && q.dim() == 4 && v.dim() == 4 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && z.stride(2) == 1,
                 "bad recurrence operands");
     const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), V = v.size(3);
-    TORCH_CHECK(q.stride(2) == D && k.stride(2) == D && v.stride(2) == V, "heads must be laid out one after another");
-    TORCH_CHECK(q.stride(0) == k.stride(0) && q.stride(0) == v.stride(0) && q.stride(1) == k.stride(1) && q.stride(1) == v.stride(1),
-                "q, k, v must share their batch and token strides");
+    TORCH_CHECK(H == 1 || (q.stride(2) == D && k.stride(2) == D && v.stride(2) == V), "heads must be laid out one after another");
+    TORCH_CHECK((B == 1 || (q.stride(0) == k.stride(0) && q.stride(0) == v.stride(0))) &&
+                    (S == 1 || (q.stride(1) == k.stride(1) && q.stride(1) == v.stride(1))),
+                "q, k, v must share their batch and token strides");   // a stride of a dimension of size 1 is never used
     TORCH_CHECK(state.is_contiguous() && state.scalar_type() == at::kFloat && state.size(1) == H && state.size(2) == D && state.size(3) == V,
                 "state must be float [slots,H,D,V]");
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() && q.scalar_type() == z.scalar_type(), "dtype mismatch");

@@ -476,9 +476,35 @@ def test_trace_runner_command_line(mixed, tmp_path):
 
 
 @pytest.mark.gpu
-def test_bfloat16_serving_close_to_the_oracle(mixed):
-    """The serving precision: bfloat16 matrix products, float statistics / states / residual.  Prompt + decode, against float64."""
-    cfg, w, toks, want, _ = mixed
+def test_bfloat16_serving_close_to_the_oracle():
+    """The serving precision: bfloat16 matrix products, float statistics / states / residual.  Prompt + decode, against float64.
+    Dense feed-forwards only: a routed layer may pick another expert on a close call in bfloat16 (covered row by row below)."""
+    cfg = make_cfg([gla_spec(mlp=DENSE), attn_spec(mlp=DENSE), lru_spec(mlp=DENSE), attn_spec(window=5, heads=2, mlp=None),
+                    gla_spec(heads=1, dim=8, vdim=24, tau=2.0, mlp=DENSE)])
+    w = random_checkpoint(cfg, seed=11)
+    toks = tokens_for(cfg, 48, 7)
+    want, _ = oracle.forward(complete_config(cfg, {k: v.shape for k, v in w.items()}), w, toks)
     model = build(cfg, w, "cuda", dtype=torch.bfloat16)
-    close(run_alone(model, toks, 20), want, 6e-2)
-    close(run_alone(model, toks, 48), want, 6e-2)
+    close(run_alone(model, toks, 20), want, 8e-2)
+    close(run_alone(model, toks, 48), want, 8e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [6, 90])
+def test_bfloat16_routed_ffn_rows_with_a_clear_choice(rows):
+    f = moe(experts=6, top=2, scale=1.7, ff=24, shared=40)
+    cfg = make_cfg([gla_spec(mlp=f)])
+    w = random_checkpoint(cfg, seed=4)
+    P = oracle.sub(w, "l0.mlp.")
+    m = RoutedFFN(cfg["width"], 24, 6, 2, weight_scale=1.7, shared_ff=40, dtype=torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        m.up.copy_(torch.stack([P[f"e{e}.up"] for e in range(6)])), m.down.copy_(torch.stack([P[f"e{e}.down"] for e in range(6)]))
+        m.router.linear_router.weight.copy_(P["router"])
+        m.shared_up.copy_(P["shared.up"]), m.shared_down.copy_(P["shared.down"])
+    h = torch.randn(rows, cfg["width"], generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    want = oracle.moe_ff(h.double(), {k: v.double() for k, v in P.items()}, f)
+    s = torch.sigmoid(h.double() @ P["router"].double().T).sort(-1, descending=True).values
+    clear = (s[:, 1] - s[:, 2]) > 0.02
+    got = m(h.cuda()).cpu().double()
+    assert clear.sum() >= rows // 2
+    assert torch.allclose(got[clear], want[clear], atol=3e-2, rtol=3e-2)
