@@ -249,7 +249,7 @@ class NaguzenForInference(nn.Module):
         self.states = SequenceStateManager(self.lm.state_specs(), num_slots=max(batch_size, 1), device=cfg.device)
         self.sampler = sampler or Sampler(top_k=1, vocab_parallel=False)
         self.on_device_sampling = on_device_sampling
-        self._rows: Optional[List[int]] = None
+        self._rows = None
 
     @classmethod
     def from_pretrained(cls, path: str, dtype: torch.dtype = torch.bfloat16, device=None, **kw) -> "NaguzenForInference":
@@ -292,26 +292,32 @@ class NaguzenForInference(nn.Module):
         return self.sampler.sample(logits) if self.on_device_sampling else logits
 
     # ---- static-batch entry points (rows ↔ slots held for the lifetime of the batch) ---------------------------------------------
-    def _batch_slots(self, B: int) -> List[int]:
-        if self._rows is None or len(self._rows) != B:
-            for s in self._rows or []:
+    def _batch_rows(self, B: int):
+        """Slots of the static batch and the constant step tensors that go with it, made once (nothing is copied from the host in
+        a token-generation step, so the step can be captured in a CUDA graph)."""
+        if self._rows is None or len(self._rows[0]) != B:
+            for s in (self._rows[0] if self._rows else []):
                 self.states.free(s)
-            self._rows = [self.states.alloc() for _ in range(B)]
+            slots = [self.states.alloc() for _ in range(B)]
+            dev = self.lm.embed.device
+            self._rows = (slots, torch.tensor(slots, dtype=torch.int32, device=dev), torch.ones(B, dtype=torch.int32, device=dev),
+                          torch.zeros(B, dtype=torch.int32, device=dev), torch.arange(B, device=dev))
         return self._rows
 
     @torch.no_grad()
     def context_encoding(self, input_ids: torch.Tensor, last_token_index: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``input_ids [B,S]`` right-padded prompts → next token ids ``[B]`` (or logits)."""
         B, S = input_ids.shape
+        _, slots, _, zeros, rows = self._batch_rows(B)
         last = last_token_index if last_token_index is not None else torch.full((B,), S - 1, device=input_ids.device)
-        x = self.forward_step(input_ids, last + 1, self._batch_slots(B), torch.zeros(B, dtype=torch.int32), True)
-        return self._pick(self.logits(x[torch.arange(B, device=x.device), last.long()]))
+        x = self.forward_step(input_ids, last + 1, slots, zeros, True)
+        return self._pick(self.logits(x[rows, last.long()]))
 
     @torch.no_grad()
     def token_generation(self, input_ids: torch.Tensor, positions: torch.Tensor, kv_len: Optional[int] = None) -> torch.Tensor:
         """``input_ids [B,1]``, ``positions [B]`` → next token ids ``[B]`` (or logits)."""
-        B = input_ids.shape[0]
-        x = self.forward_step(input_ids, torch.ones(B, dtype=torch.int32), self._batch_slots(B), positions, False)
+        _, slots, ones, _, _ = self._batch_rows(input_ids.shape[0])
+        x = self.forward_step(input_ids, ones, slots, positions, False)
         return self._pick(self.logits(x[:, 0]))
 
     @torch.no_grad()

@@ -1,0 +1,258 @@
+"""``bench.py --mode naguzen``: serving throughput of the Naguzen design at layer sizes that resemble a real model (random weights),
+beside the framework's closest existing model — Llama through ``LlamaForInference`` — at equal width, depth and feed-forward
+parameter count; plus every sequence-mixer kernel timed alone against the measured copy bandwidth / GEMM throughput, beside the
+like kernel of the Llama path.  One GPU, bfloat16.  Device time (CUDA events), >= 3 warm-up iterations; the weights of either
+model (> 1 GB) exceed L2, and the kernel timings flush L2 (a 512 MiB write) between iterations.
+
+Layers: latent attention + dense | gla + routed | rglru + dense | latent attention + routed, width 2048: attention 16 heads of
+128 + 64 rotated, value 128, latents 512 / 1536, window 1024; gla 4 heads, key 256, value 512; rglru width 2048 in 8 blocks;
+dense ff 8192; 32 experts of ff 1024, top 4, shared ff 2048.  Llama: 4 layers, width 2048, 16 heads of 128 (4 KV heads), ff 5504."""
+from __future__ import annotations
+
+import json
+import math
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+WIDTH, VOCAB = 2048, 32000
+
+
+def naguzen_layers():
+    att = lambda mlp: {"type": "latent_attention", "mlp": mlp,
+                       "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "mask": {"size": 1024},
+                                 "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192)}}
+    dense = {"kind": "dense", "ff": 8192}
+    moe = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4, "scale": 2.5}, "shared": {"ff": 2048}}
+    return [att(dense),
+            {"type": "gla", "mlp": moe, "mixer": {"heads": 4, "dim": 256, "vdim": 512, "tau": 16.0, "decay_rank": 16}},
+            {"type": "rglru", "mlp": dense, "mixer": {"width": 2048, "blocks": 8, "conv": 4}},
+            att(moe)]
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def _timed(fn, steps, warmup, flush=None):
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.fill_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b))
+    ms.sort()
+    return ms[len(ms) // 2]
+
+
+def build_naguzen(dev, batch, max_len):
+    import torch
+
+    from neuronx_distributed_b200.models.naguzen import NaguzenConfig, NaguzenForInference
+
+    cfg = NaguzenConfig(vocab=VOCAB, width=WIDTH, layers=naguzen_layers(), norm_eps=1e-6, canon_taps=4, dtype=torch.bfloat16, device=dev)
+    m = NaguzenForInference(cfg, batch_size=batch, max_seq_len=max_len).eval()
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if p.dtype == torch.bfloat16 or "router" in name or "gate_" in name and "bias" not in name:
+                p.normal_(0.0, 0.02 if p.dim() > 1 else 0.0, generator=g)
+            elif name.endswith(("norm.weight", "norm1.weight", "norm2.weight", "dq_norm", "dkv_norm", "mixer.norm")):
+                p.fill_(1.0)
+            elif "a2_bias" in name:
+                p.fill_(3.0)
+            elif "lam_softplus" in name:
+                p.fill_(0.05)
+            elif "canon" in name or "conv.weight" in name:
+                p.normal_(0.0, 0.2, generator=g)
+        m.lm.embed.normal_(0.0, 1.0, generator=g)
+    for mod in m.modules():
+        if hasattr(mod, "set_activation"):
+            mod.set_activation(torch.tensor([0.3, -0.4]))
+    return m
+
+
+def build_llama(dev, batch, max_len):
+    import torch
+
+    from neuronx_distributed_b200.models.llama import LlamaConfig
+    from neuronx_distributed_b200.models.llama_inference import LlamaForInference
+
+    cfg = LlamaConfig(vocab_size=VOCAB, hidden_size=WIDTH, intermediate_size=5504, num_hidden_layers=4, num_attention_heads=16,
+                      num_key_value_heads=4, dtype=torch.bfloat16, device=dev, max_position_embeddings=max_len)
+    torch.manual_seed(0)
+    return LlamaForInference(cfg, batch_size=batch, max_seq_len=max_len).eval()
+
+
+def throughput(model, dev, B, S, decode_from, steps, warmup, graphs=True):
+    """Prompt tokens/s of one ``context_encoding`` call at ``[B,S]`` and generated tokens/s of ``token_generation`` at batch B."""
+    import torch
+
+    ids = torch.randint(0, VOCAB, (B, S), device=dev)
+    last = torch.full((B,), S - 1, dtype=torch.long, device=dev)
+    pre_ms = _timed(lambda: model.context_encoding(ids, last), steps, warmup)
+    tok = torch.randint(0, VOCAB, (B, 1), device=dev)
+    pos = torch.full((B,), decode_from, dtype=torch.long, device=dev)
+    step = lambda: model.token_generation(tok, pos)
+    captured = False
+    if graphs:
+        try:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(3):
+                    step()
+            torch.cuda.current_stream().wait_stream(s)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                out = step()
+            step, captured = gr.replay, True
+        except Exception as e:                                   # reported, not hidden: the eager step is timed instead
+            print(json.dumps({"graph_capture_failed": f"{type(e).__name__}: {str(e)[:200]}"}), flush=True)
+            torch.cuda.synchronize()
+            step = lambda: model.token_generation(tok, pos)
+    dec_ms = _timed(step, max(steps, 20), max(warmup, 5))
+    return {"prefill_tokens_per_s": B * S / pre_ms * 1e3, "prefill_ms": pre_ms, "decode_tokens_per_s": B / dec_ms * 1e3,
+            "decode_ms_per_step": dec_ms, "decode_cuda_graph": captured, "batch": B, "prompt": S, "decode_position": decode_from}
+
+
+def kernel_table(dev, steps, warmup):
+    """Each kernel alone at the sizes of the model above (4 x 2048 prompt tokens; 8 decoding rows) → time, achieved GB/s or
+    TFLOP/s, fraction of the measured peak.  Llama's like kernels are timed the same way."""
+    import torch
+
+    from neuronx_distributed_b200 import ops
+    from neuronx_distributed_b200.ops import seqmix
+
+    hbm, tfl, src = _peaks()
+    flush = torch.empty(128 << 20, dtype=torch.float32, device=dev)
+    bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    B, S, W = 4, 2048, WIDTH
+    N = B * S
+    rnd = lambda *s, dtype=bf: torch.randn(*s, device=dev, dtype=f32).to(dtype)
+    lens, slots, pos0 = torch.full((B,), S, dtype=i32, device=dev), torch.arange(B, dtype=i32, device=dev), torch.zeros(B, dtype=i32, device=dev)
+    rows = []
+
+    def add(name, fn, bytes_=0, flops=0, like=None):
+        ms = _timed(fn, steps, warmup, flush)
+        r = {"kernel": name, "ms": round(ms, 4)}
+        if bytes_:
+            r["gbs"] = round(bytes_ / ms / 1e6, 1)
+            r["frac_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+            r["frac_bf16_gemm"] = round(flops / ms / 1e9 / tfl, 4)
+        if like:
+            r["like"] = like
+        rows.append(r)
+
+    x32, y16 = rnd(B, S, W, dtype=f32), rnd(B, S, W)
+    cw, st32 = rnd(W, 4, dtype=f32), torch.zeros(B, 3, W, dtype=f32, device=dev)
+    add("short_conv residual f32->bf16", lambda: seqmix.short_conv(x32, cw, None, st32, slots, lens, True, True, bf), N * W * 6)
+    one, vec = torch.ones(1, device=dev), torch.ones(W, device=dev)
+    add("add_rms_norm_ (scalar gain, f32 residual)", lambda: seqmix.add_rms_norm_(x32.view(N, W), y16.view(N, W), one, 1e-6), N * W * 10)
+    add("rms_norm bf16->bf16 (vector gain)", lambda: seqmix.rms_norm(y16.view(N, W), vec, 1e-6), N * W * 4)
+    wl = torch.ones(W, device=dev, dtype=bf)
+    add("llama rms_norm bf16", lambda: ops.norm.rms_norm(y16.view(N, W), wl, 1e-6), N * W * 4, like="rms_norm / add_rms_norm_")
+    up = rnd(N, 8192)
+    add("xielu [N,8192]", lambda: seqmix.xielu(up, 0.8, 1.0), N * 8192 * 4)
+    gu = rnd(N, 2 * 5504)
+    add("llama swiglu [N,2x5504]", lambda: ops.act.swiglu(gu), N * 5504 * 6, like="xielu / gelu_erf")
+    # latent attention pieces
+    H, D, R, C, win = 16, 128, 64, 512, 1024
+    kv, nw, inv = rnd(B, S, C + R), torch.ones(C, device=dev), seqmix.rotary_inv_freq(R, 10000.0, dev)
+    cache = torch.zeros(B, win, C + R, dtype=bf, device=dev)
+    add("latent_kv_store (norm + rope + ring append)", lambda: seqmix.latent_kv_store(kv, nw, 1e-6, inv, R, pos0, lens, slots, cache, True),
+        N * (C + R) * 4 + B * win * (C + R) * 2)
+    q = rnd(B, S, H, D + R)
+    add("rope_q_ (64 of 192 dims, in place)", lambda: seqmix.rope_q_(q, D, R, inv, pos0), N * H * R * 4)
+    ql = rnd(B, S, H, 128)
+    cos, sin = ops.rope.rope_tables(S, 128, 10000.0, dev)
+    add("llama apply_rotary [B,S,16,128]", lambda: ops.rope.apply_rotary(ql, cos, sin), N * H * 128 * 4, like="rope_q_ / latent_kv_store")
+    qa, keys = rnd(H, N, C), rnd(B, S, C + R)
+    pairs = B * H * sum(min(p + 1, win) for p in range(S))
+    add("latent_window_attention prompt (window 1024)", lambda: seqmix.latent_window_attention(qa, q, D, keys, None, pos0, lens, win, 0.07),
+        flops=pairs * (2 * (C + R) + 2 * C))
+    qf, kf, vf = rnd(B, S, H, 128), rnd(B, S, 4, 128), rnd(B, S, 4, 128)
+    add("llama flash_attention prompt (causal, full)", lambda: ops.attention.flash_attention(qf, kf, vf, causal=True),
+        flops=4 * B * H * 128 * S * (S + 1) / 2, like="latent_window_attention prompt")
+    Bd = 8
+    qa1, q1 = rnd(H, Bd, C), rnd(Bd, 1, H, D + R)
+    cache8 = rnd(Bd, win, C + R)
+    l1, s8, p8 = torch.ones(Bd, dtype=i32, device=dev), torch.arange(Bd, dtype=i32, device=dev), torch.full((Bd,), 2047, dtype=i32, device=dev)
+    add("latent_window_attention decode (8 rows, ring 1024)", lambda: seqmix.latent_window_attention(qa1, q1, D, cache8, s8, p8, l1, win, 0.07),
+        bytes_=Bd * win * (C + R) * 2)
+    e = ops._ext.ext()
+    if e is not None and hasattr(e, "decode_attention"):
+        qd, kc, vc = rnd(Bd, 1, H, 128), rnd(Bd, 2048, 4, 128), rnd(Bd, 2048, 4, 128)
+        pl = torch.full((Bd,), 2047, dtype=torch.long, device=dev)
+        add("llama decode_attention (8 rows, 2048 keys, 4 KV heads)", lambda: e.decode_attention(qd, kc, vc, pl, 1.0 / math.sqrt(128)),
+            bytes_=Bd * 2048 * 4 * 128 * 4, like="latent_window_attention decode")
+    # recurrences
+    Hg, Dg, Vg = 4, 256, 512
+    p = rnd(B, S, 2 * Hg * Dg + Hg * Vg)
+    qg, kg = p[..., :Hg * Dg].unflatten(-1, (Hg, Dg)), p[..., Hg * Dg:2 * Hg * Dg].unflatten(-1, (Hg, Dg))
+    vg, z = p[..., 2 * Hg * Dg:].unflatten(-1, (Hg, Vg)), rnd(B, S, Hg * Dg)
+    zb, stg = torch.full((Hg * Dg,), 3.0, device=dev), torch.zeros(B, Hg, Dg, Vg, device=dev)
+    add("gla_scan prompt (4 heads, 256 x 512 state)", lambda: seqmix.gla_scan(qg, kg, vg, z, zb, 16.0, stg, slots, lens, True),
+        bytes_=N * (3 * Hg * Dg * 2 + Hg * Vg * 2 + Hg * Vg * 4), flops=N * Hg * Dg * Vg * 4)
+    p1, z1, st8 = rnd(Bd, 1, 2 * Hg * Dg + Hg * Vg), rnd(Bd, 1, Hg * Dg), torch.zeros(Bd, Hg, Dg, Vg, device=dev)
+    q1g, k1g = p1[..., :Hg * Dg].unflatten(-1, (Hg, Dg)), p1[..., Hg * Dg:2 * Hg * Dg].unflatten(-1, (Hg, Dg))
+    v1g = p1[..., 2 * Hg * Dg:].unflatten(-1, (Hg, Vg))
+    add("gla_scan decode (8 rows)", lambda: seqmix.gla_scan(q1g, k1g, v1g, z1, zb, 16.0, st8, s8, l1, False), bytes_=Bd * Hg * Dg * Vg * 8)
+    RW, nb = 2048, 8
+    u, yv = rnd(B, S, RW), rnd(B, S, RW)
+    gr, gi = rnd(nb, N, RW // nb, dtype=f32), rnd(nb, N, RW // nb, dtype=f32)
+    zr, lam, sth = torch.zeros(RW, device=dev), torch.full((RW,), 0.05, device=dev), torch.zeros(B, RW, device=dev)
+    add("rglru_scan prompt (2048 channels)", lambda: seqmix.rglru_scan(u, gr, gi, zr, zr, lam, yv, sth, slots, lens, True), bytes_=N * RW * 14)
+    # routed small batch
+    E, ff, top = 32, 1024, 4
+    wu, xs = rnd(E, ff, W), rnd(Bd * top, W)
+    sel = torch.randint(0, E, (Bd * top,), device=dev, dtype=i32)
+    add("indexed_gemv up+gelu (32 rows x expert [1024,2048])", lambda: seqmix.indexed_gemv(wu, sel, xs, True), bytes_=Bd * top * ff * W * 2)
+    return {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}, "rows": rows}
+
+
+def main(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29537")
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    from neuronx_distributed_b200.parallel_layers import parallel_state as ps
+
+    ps.initialize_model_parallel(tensor_model_parallel_size=1)
+    steps, warmup = max(3, args.steps), max(3, args.warmup)
+    out = {"mode": "naguzen", "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup, "n_gpus": 1,
+           "l2": "weights of either model exceed L2; kernel rows flush L2 between iterations"}
+    shapes = [(4, 2048), (1, 8192), (8, 512)]
+    for name, make in (("naguzen", build_naguzen), ("llama", build_llama)):
+        res = []
+        for B, S in shapes:
+            model = make(dev, B, S + 64)
+            res.append(throughput(model, dev, B, S, S, steps, warmup))
+            del model
+            torch.cuda.empty_cache()
+        out[name] = res
+    out["kernels"] = kernel_table(dev, max(steps, 5), warmup)
+    print(json.dumps(out), flush=True)
+    dist.destroy_process_group()
+    return 0
