@@ -114,6 +114,58 @@ __global__ void latent_window_attn_kernel(const T* __restrict__ qa, long qa_sn, 
     }
 }
 
+// Softmax over the visible keys of score rows produced by block matrix products (float in, activation dtype out, zeros where masked).
+//   band mode: rows are (sequence b, query block, token t in block, head); column kk of a row holds position
+//              j = blk*Qb - (w_eff - 1) + kk of the same sequence; visible: 0 <= j <= i and j > i - window, i = blk*Qb + t.
+//   ring mode: rows are (sequence b, head) of one new token at position p = pos0[b]; column kk is ring row kk, which holds position
+//              j = p - ((p - kk) mod ring); visible: j >= 0 and p - j < window.
+template <typename Tout, bool RING>
+__global__ void window_softmax_kernel(const float* __restrict__ scores, long rows, int span, float scale, int H, int Qb, int nblk, int w_eff,
+                                      int window, const int* __restrict__ pos0, const int* __restrict__ lens, Tout* __restrict__ out) {
+    const long r = (long)blockIdx.x * blockDim.y + threadIdx.y;
+    const int lane = threadIdx.x;
+    if (r >= rows) return;
+    const float* sr = scores + r * span;
+    Tout* orow = out + r * span;
+    int b, i, j0;
+    if (RING) { b = (int)(r / H); i = pos0[b]; j0 = 0; }
+    else {
+        const int t = (int)((r / H) % Qb), blk = (int)((r / ((long)H * Qb)) % nblk);
+        b = (int)(r / ((long)H * Qb * nblk));
+        i = blk * Qb + t;
+        j0 = blk * Qb - (w_eff - 1);
+    }
+    const bool live = RING ? lens[b] > 0 : i < lens[b];
+    auto visible = [&](int kk) -> bool {
+        if (RING) { int m = (i - kk) % span; if (m < 0) m += span; return i - m >= 0 && m < window; }
+        const int j = j0 + kk;
+        return j >= 0 && j <= i && j > i - window;
+    };
+    float mx = -INFINITY;
+    if (live)
+        for (int kk = lane; kk < span; kk += 32)
+            if (visible(kk)) mx = fmaxf(mx, sr[kk] * scale);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    if (live)
+        for (int kk = lane; kk < span; kk += 32)
+            if (visible(kk)) sum += expf(sr[kk] * scale - mx);
+    sum = warp_sum(sum);
+    const float inv = live ? 1.f / sum : 0.f;
+    for (int kk = lane; kk < span; kk += 32) stf(orow + kk, (live && visible(kk)) ? expf(sr[kk] * scale - mx) * inv : 0.f);
+}
+
+void window_softmax(const float* scores, long rows, int span, float scale, int ring_mode, int H, int Qb, int nblk, int w_eff, int window,
+                    const int* pos0, const int* lens, void* out, int out_bf16, cudaStream_t s) {
+    if (rows == 0) return;
+    dim3 block(32, 8), grid((unsigned)((rows + 7) / 8));
+#define SEQMIX_SM(T, R) window_softmax_kernel<T, R><<<grid, block, 0, s>>>(scores, rows, span, scale, H, Qb, nblk, w_eff, window, pos0, lens, (T*)out)
+    if (out_bf16) { if (ring_mode) SEQMIX_SM(bf16, true); else SEQMIX_SM(bf16, false); }
+    else { if (ring_mode) SEQMIX_SM(float, true); else SEQMIX_SM(float, false); }
+#undef SEQMIX_SM
+}
+
 void latent_kv_store(const void* kv, int bf, long kv_sb, long kv_st, int B, int S, int C, int R, int dims, const float* nw, float eps,
                      const float* inv_freq, const int* pos0, const int* lens, const int* slots, void* cache, int ring, void* rows,
                      cudaStream_t s) {

@@ -11,18 +11,21 @@
 
 namespace seqmix {
 
-constexpr int kStage = 8;   // staged loads per thread and token
+constexpr int kStage = 32;  // staged loads per thread and barrier
+constexpr int kSteps = 8;   // tokens staged per barrier
 
+// Shared-memory image of one token: float4 {alpha, k, q, -} per key channel, then the slice's Vb values.
 template <typename T, int DPT>
 __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long sb, long st,
                                 const T* __restrict__ z, long z_sb, long z_st, const float* __restrict__ zbias, float inv_tau,
                                 float qscale, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh,
-                                int S, int H, int D, int V, int R, int Vb, float* __restrict__ out) {
-    extern __shared__ float sm[];
+                                int S, int H, int D, int V, int R, int Vb, int TB, float* __restrict__ out) {
+    extern __shared__ float4 sm4[];
+    float* sm = reinterpret_cast<float*>(sm4);
     const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * Vb;
-    const int tid = threadIdx.x, nthr = blockDim.x, r = tid % R, j = j0 + tid / R;
-    const int len = min(lens[b], S), per = 3 * D + Vb;
-    const bool live = tid / R < Vb && j < V;
+    const int tid = threadIdx.x, nthr = blockDim.x, r = tid % R, jl = tid / R, j = j0 + jl;
+    const int len = min(lens[b], S), per = 4 * D + ((Vb + 3) & ~3), chunk = TB * per;
+    const bool live = jl < Vb && j < V;
     float s[DPT];
     float* sp = state + (((long)slots[b] * H + h) * D) * V;
 #pragma unroll
@@ -31,47 +34,61 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
         s[i] = (!fresh && live && d < D) ? sp[(long)d * V + j] : 0.f;
     }
     const long hq = (long)h * D, hv = (long)h * V + j0;
-    auto fetch = [&](int t, int e) -> float {
+    // element e of a chunk that starts at token t0: token t0 + e / per, field e % per
+    auto fetch = [&](int t0, int e) -> float {
+        const int t = t0 + e / per, f = e % per;
+        if (t >= len) return 0.f;
         const long tok = (long)b * sb + (long)t * st;
-        if (e < D) {
-            float zz = ldf(z + (long)b * z_sb + (long)t * z_st + hq + e) + zbias[hq + e];
-            return 1.f + expm1f(log_sigmoidf_(zz) * inv_tau);   // rounds once from an accurate value: no bias as alpha -> 1
+        if (f < 4 * D) {
+            const int d = f >> 2, w = f & 3;
+            if (w == 0) {
+                float zz = ldf(z + (long)b * z_sb + (long)t * z_st + hq + d) + zbias[hq + d];
+                return 1.f + expm1f(log_sigmoidf_(zz) * inv_tau);   // rounds once from an accurate value: no bias as alpha -> 1
+            }
+            if (w == 1) return ldf(k + tok + hq + d);
+            if (w == 2) return ldf(q + tok + hq + d) * qscale;
+            return 0.f;
         }
-        if (e < 2 * D) return ldf(k + tok + hq + e - D);
-        if (e < 3 * D) return ldf(q + tok + hq + e - 2 * D) * qscale;
-        return (j0 + e - 3 * D < V) ? ldf(v + tok + hv + e - 3 * D) : 0.f;
+        return (j0 + f - 4 * D < V) ? ldf(v + tok + hv + f - 4 * D) : 0.f;
     };
-    if (len > 0)
-        for (int e = tid; e < per; e += nthr) sm[e] = fetch(0, e);
-    for (int t = 0; t < len; ++t) {
-        float* cur = sm + (t & 1) * per;
-        float* nxt = sm + ((t + 1) & 1) * per;
+    for (int e = tid; e < chunk; e += nthr) sm[e] = fetch(0, e);
+    const int nchunks = (len + TB - 1) / TB;
+    for (int c = 0; c < nchunks; ++c) {
+        const float* cur = sm + (c & 1) * chunk;
+        float* nxt = sm + ((c + 1) & 1) * chunk;
         __syncthreads();
         float stage[kStage];
-        if (t + 1 < len) {
+        const bool more = c + 1 < nchunks;
+        if (more) {
 #pragma unroll
             for (int x = 0; x < kStage; ++x) {
                 const int e = tid + x * nthr;
-                stage[x] = e < per ? fetch(t + 1, e) : 0.f;
+                stage[x] = e < chunk ? fetch((c + 1) * TB, e) : 0.f;
             }
         }
-        const float vj = live ? cur[3 * D + tid / R] : 0.f;
-        float acc = 0.f;
+        const int steps = min(TB, len - c * TB);
+        for (int u = 0; u < steps; ++u) {
+            const float* tokp = cur + u * per;
+            const float4* akq = reinterpret_cast<const float4*>(tokp);
+            const float vj = live ? tokp[4 * D + jl] : 0.f;
+            float acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            const int d = r + i * R;
-            if (d < D) {
-                s[i] = fmaf(cur[d], s[i], cur[D + d] * vj);
-                acc = fmaf(s[i], cur[2 * D + d], acc);
+            for (int i = 0; i < DPT; ++i) {
+                const int d = r + i * R;
+                if (d < D) {
+                    const float4 a = akq[d];
+                    s[i] = fmaf(a.x, s[i], a.y * vj);
+                    acc = fmaf(s[i], a.z, acc);
+                }
             }
+            for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (r == 0 && live) out[(((long)b * S + c * TB + u) * H + h) * V + j] = acc;
         }
-        for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (r == 0 && live) out[(((long)b * S + t) * H + h) * V + j] = acc;
-        if (t + 1 < len) {
+        if (more) {
 #pragma unroll
             for (int x = 0; x < kStage; ++x) {
                 const int e = tid + x * nthr;
-                if (e < per) nxt[e] = stage[x];
+                if (e < chunk) nxt[e] = stage[x];
             }
         }
     }
@@ -92,24 +109,36 @@ template <typename T>
 static bool gla_launch(const void* q, const void* k, const void* v, long sb, long st, const void* z, long z_sb, long z_st,
                        const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh,
                        int B, int S, int H, int D, int V, float* out, cudaStream_t s) {
-    const int dpts[3] = {8, 16, 32};
+    // fewer, fatter blocks (more state rows per thread) as long as the grid still fills the GPU: the step's alpha / k / q are
+    // prepared once per block, so every extra slice of value columns repeats that work
+    const int dpts[3] = {32, 16, 8};
+    int pick = -1, pR = 0, pVb = 0;
     for (int a = 0; a < 3; ++a) {
         const int DPT = dpts[a], R = pow2ceil((D + DPT - 1) / DPT);
         if (R > 32) continue;
         int Vb = 256 / R; if (Vb < 1) Vb = 1; if (Vb > V) Vb = V;
-        int threads = R * Vb;
-        threads = ((threads + 31) / 32) * 32;
-        if (3 * D + Vb > kStage * threads) continue;
-        dim3 grid(H, B, (V + Vb - 1) / Vb);
-        const size_t smem = 2 * (size_t)(3 * D + Vb) * sizeof(float);
-#define SEQMIX_GLA(P)                                                                                                             \
-    gla_scan_kernel<T, P><<<grid, threads, smem, s>>>((const T*)q, (const T*)k, (const T*)v, sb, st, (const T*)z, z_sb, z_st, zbias,  \
-                                                      inv_tau, qscale, state, slots, lens, fresh, S, H, D, V, R, Vb, out)
-        if (DPT == 8) SEQMIX_GLA(8); else if (DPT == 16) SEQMIX_GLA(16); else SEQMIX_GLA(32);
-#undef SEQMIX_GLA
-        return true;
+        const long blocks = (long)H * B * ((V + Vb - 1) / Vb);
+        if (pick < 0 || blocks >= 148) { pick = DPT; pR = R; pVb = Vb; }
+        if (blocks >= 148) break;
     }
-    return false;
+    if (pick < 0) return false;
+    const int R = pR, Vb = pVb;
+    int threads = ((R * Vb + 31) / 32) * 32;
+    const int per = 4 * D + ((Vb + 3) & ~3);
+    int TB = S < kSteps ? (S < 1 ? 1 : S) : kSteps;
+    while (TB > 1 && ((long)TB * per > (long)kStage * threads || 2L * TB * per * 4 > 96 * 1024)) --TB;
+    if ((long)TB * per > (long)kStage * threads || 2L * TB * per * 4 > 96 * 1024) return false;
+    dim3 grid(H, B, (V + Vb - 1) / Vb);
+    const size_t smem = 2 * (size_t)TB * per * sizeof(float);
+#define SEQMIX_GLA(P)                                                                                                             \
+    do {                                                                                                                          \
+        cudaFuncSetAttribute(gla_scan_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);                      \
+        gla_scan_kernel<T, P><<<grid, threads, smem, s>>>((const T*)q, (const T*)k, (const T*)v, sb, st, (const T*)z, z_sb, z_st,    \
+                                                          zbias, inv_tau, qscale, state, slots, lens, fresh, S, H, D, V, R, Vb, TB, out); \
+    } while (0)
+    if (pick == 8) SEQMIX_GLA(8); else if (pick == 16) SEQMIX_GLA(16); else SEQMIX_GLA(32);
+#undef SEQMIX_GLA
+    return true;
 }
 
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
@@ -119,21 +148,40 @@ bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long
               : gla_launch<float>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, state, slots, lens, fresh, B, S, H, D, V, out, s);
 }
 
+// One block = 32 channels of one sequence x TY time lanes.  Each lane scans its slice of the tokens from zero keeping the product of
+// its decays; the carries are folded through shared memory; the lanes scan again from their true carry and write the outputs.
 template <typename T>
 __global__ void rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ gr, const float* __restrict__ gi, int wb,
                                   const float* __restrict__ rbias, const float* __restrict__ ibias, const float* __restrict__ lam_sp,
                                   const T* __restrict__ y, long y_sb, long y_st, float* state, const int* __restrict__ slots,
                                   const int* __restrict__ lens, int fresh, int B, int S, int W, T* __restrict__ out) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
-    if (c >= W) return;
+    __shared__ float sA[32][33], sH[32][33];
+    const int c = blockIdx.x * 32 + threadIdx.x, b = blockIdx.y, ty = threadIdx.y, TY = blockDim.y;
     const int len = min(lens[b], S);
+    const int L = (len + TY - 1) / TY, t0 = min(len, ty * L), t1 = min(len, t0 + L);
+    const bool on = c < W;
     const long N = (long)B * S;
-    const long gbase = ((long)(c / wb) * N + (long)b * S) * wb + c % wb;       // gates are laid out [block, token, channel in block]
-    const float rb = rbias[c], ib = ibias[c], sp = lam_sp[c];
-    float* hs = state + (long)slots[b] * W + c;
-    float h = fresh ? 0.f : *hs;
+    const long gbase = on ? ((long)(c / wb) * N + (long)b * S) * wb + c % wb : 0;   // gates: [block, token, channel in block]
+    const float rb = on ? rbias[c] : 0.f, ib = on ? ibias[c] : 0.f, sp = on ? lam_sp[c] : 0.f;
+    float A = 1.f, h = 0.f;
+    if (on && TY > 1) {
 #pragma unroll 4
-    for (int t = 0; t < len; ++t) {
+        for (int t = t0; t < t1; ++t) {
+            const float r = sigmoidf_(gr[gbase + (long)t * wb] + rb), g = sigmoidf_(gi[gbase + (long)t * wb] + ib);
+            const float la = -8.f * r * sp, a = 1.f + expm1f(la), mult = sqrtf(-expm1f(2.f * la));
+            h = fmaf(a, h, mult * g * ldf(u + ((long)b * S + t) * W + c));
+            A *= a;
+        }
+    }
+    sA[ty][threadIdx.x] = A;
+    sH[ty][threadIdx.x] = h;
+    __syncthreads();
+    if (!on) return;
+    float* hs = state + (long)slots[b] * W + c;
+    h = fresh ? 0.f : *hs;
+    for (int k = 0; k < ty; ++k) h = fmaf(sA[k][threadIdx.x], h, sH[k][threadIdx.x]);
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
         const float r = sigmoidf_(gr[gbase + (long)t * wb] + rb), g = sigmoidf_(gi[gbase + (long)t * wb] + ib);
         const float uu = ldf(u + ((long)b * S + t) * W + c), yy = ldf(y + (long)b * y_sb + (long)t * y_st + c);
         const float la = -8.f * r * sp, a = 1.f + expm1f(la), mult = sqrtf(-expm1f(2.f * la));
@@ -141,14 +189,16 @@ __global__ void rglru_scan_kernel(const T* __restrict__ u, const float* __restri
         const float gl = 0.5f * yy * (1.f + tanhf(0.7978845608028654f * (yy + 0.044715f * yy * yy * yy)));
         stf(out + ((long)b * S + t) * W + c, h * gl);
     }
-    for (int t = len; t < S; ++t) stf(out + ((long)b * S + t) * W + c, 0.f);
-    *hs = h;
+    for (int t = len + ty; t < S; t += TY) stf(out + ((long)b * S + t) * W + c, 0.f);
+    if (ty == TY - 1) *hs = h;      // the last lane's slice ends at the sequence's last token (an empty slice passes the carry on)
 }
 
 void rglru_scan(const void* u, int bf, const float* gr, const float* gi, int wb, const float* rbias, const float* ibias,
                 const float* lam_sp, const void* y, long y_sb, long y_st, float* state, const int* slots, const int* lens, int fresh,
                 int B, int S, int W, void* out, cudaStream_t s) {
-    dim3 block(128), grid((W + 127) / 128, B);
+    int ty = 1;
+    while (ty < 32 && ty * 16 < S) ty <<= 1;
+    dim3 block(32, ty), grid((W + 31) / 32, B);
     if (bf) rglru_scan_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)u, gr, gi, wb, rbias, ibias, lam_sp, (const bf16*)y, y_sb, y_st,
                                                           state, slots, lens, fresh, B, S, W, (bf16*)out);
     else rglru_scan_kernel<float><<<grid, block, 0, s>>>((const float*)u, gr, gi, wb, rbias, ibias, lam_sp, (const float*)y, y_sb, y_st,

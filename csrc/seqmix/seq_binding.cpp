@@ -119,6 +119,20 @@ Tensor latent_window_attention(const Tensor& qa, const Tensor& q, int64_t off, c
     return out;
 }
 
+// scores float [..., span] (contiguous) → softmax over the visible keys, in `out_bf16`'s dtype.  Band mode: rows (b, block, t, head);
+// ring mode: rows (b, head) of single tokens at positions pos0.
+Tensor window_softmax(const Tensor& scores, double scale, bool ring_mode, int64_t H, int64_t Qb, int64_t nblk, int64_t w_eff, int64_t window,
+                      const Tensor& pos0, const Tensor& lens, bool out_bf16) {
+    TORCH_CHECK(scores.is_cuda() && scores.is_contiguous() && scores.scalar_type() == at::kFloat, "scores must be contiguous float");
+    const int span = scores.size(-1);
+    const long rows = scores.numel() / span;
+    Tensor out = at::empty(scores.sizes(), scores.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+    seqmix::window_softmax(scores.data_ptr<float>(), rows, span, (float)scale, ring_mode, (int)H, (int)Qb, (int)nblk, (int)w_eff, (int)window,
+                           i32(pos0), i32(lens), out.data_ptr(), out_bf16, stream());
+    check_launch();
+    return out;
+}
+
 // q,k [B,S,H,D], v [B,S,H,V] (views with equal batch / token strides), z [B,S,H*D] → o float [B,S,H,V]; state [slots,H,D,V] float
 Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const Tensor& zbias, double tau, Tensor state,
                 const Tensor& slots, const Tensor& lens, bool fresh) {
@@ -200,6 +214,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("latent_kv_store", &latent_kv_store);
     m.def("rope_q_", &rope_q_);
     m.def("latent_window_attention", &latent_window_attention);
+    m.def("window_softmax", &window_softmax);
     m.def("gla_scan", &gla_scan);
     m.def("rglru_scan", &rglru_scan);
     m.def("xielu", &xielu);

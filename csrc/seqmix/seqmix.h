@@ -15,6 +15,8 @@ void rope_q(void* q, int bf, long q_sn, long q_sh, int N, int S, int H, int dims
 void latent_window_attention(const void* qa, int bf, long qa_sn, long qa_sh, const void* qr, long qr_sn, long qr_sh, const void* keys,
                              long key_sb, int ring, const int* key_index, const int* pos0, const int* lens, int B, int S, int H, int C,
                              int R, int window, float scale, void* out, long out_sn, long out_sh, cudaStream_t s);
+void window_softmax(const float* scores, long rows, int span, float scale, int ring_mode, int H, int Qb, int nblk, int w_eff, int window,
+                    const int* pos0, const int* lens, void* out, int out_bf16, cudaStream_t s);
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
               const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int S,
               int H, int D, int V, float* out, cudaStream_t s);

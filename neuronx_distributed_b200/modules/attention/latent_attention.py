@@ -21,11 +21,12 @@ from ...ops import seqmix
 class LatentWindowAttention(nn.Module):
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, window: int,
                  scale: float, rot_base: float, rot_dims: int, eps: float, dtype: torch.dtype = torch.bfloat16, device=None,
-                 max_seq_len: int = 1 << 30):
+                 max_seq_len: int = 1 << 30, block_products: bool = True, query_block: int = 128):
         super().__init__()
         self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank, self.q_rank = heads, dim, rot_dim, vdim, kv_rank, q_rank
         self.window, self.scale, self.rot_dims, self.eps, self.dtype = window, scale, rot_dims, eps, dtype
         self.ring = max(1, min(window, max_seq_len))
+        self.block_products, self.query_block = block_products, query_block
         self.max_seq_len = max_seq_len
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
         f32 = lambda *s: nn.Parameter(torch.ones(*s, dtype=torch.float32, device=device), requires_grad=False)
@@ -48,9 +49,36 @@ class LatentWindowAttention(nn.Module):
                                       want_rows=ctx.fresh)
         seqmix.rope_q_(q, D, self.rot_dims, self.inv_freq, ctx.pos0)
         qa = torch.bmm(q.view(N, H, D + R)[:, :, :D].transpose(0, 1), self.uk)                       # [H,N,D] @ [H,D,C]
-        if ctx.fresh:
+        if self.block_products:
+            o = self._attend_products(qa, q, rows, ctx, st)
+        elif ctx.fresh:
             o = seqmix.latent_window_attention(qa, q, D, rows, None, ctx.pos0, ctx.lens, self.window, self.scale)
         else:
             o = seqmix.latent_window_attention(qa, q, D, st["kv"], ctx.slots, ctx.pos0, ctx.lens, self.window, self.scale)
         ov = torch.bmm(o, self.uv.transpose(1, 2))                                                     # [H,N,C] @ [H,C,V]
         return F.linear(ov.transpose(0, 1).reshape(N, H * self.vdim), self.o).view(B, S, -1)
+
+    def _attend_products(self, qa: torch.Tensor, q: torch.Tensor, rows, ctx, st) -> torch.Tensor:
+        """Scores and weighted sums as matrix products with the heads folded into the row dimension (all heads share the keys):
+        a prompt is cut into blocks of ``query_block`` tokens, each multiplied with the ``query_block + window - 1`` key rows it can
+        see; a single token multiplies its sequence's ring.  The softmax over the visible keys runs in float in between
+        (``window_softmax``).  Returns ``[H, N, C]``."""
+        B, S, H, _ = q.shape
+        C, R, D = self.kv_rank, self.rot_dim, self.dim
+        qcat = torch.cat([qa.view(H, B, S, C).permute(1, 2, 0, 3), q[..., D:]], -1)                   # [B,S,H,C+R]
+        if not ctx.fresh:
+            kc = st["kv"].index_select(0, ctx.slots.long())                                            # [B,ring,C+R]
+            sc = seqmix.matmul_f32(qcat.view(B, H, C + R), kc.transpose(1, 2))                         # [B,H,ring]
+            p = seqmix.window_softmax(sc, self.scale, True, H, 1, 1, 1, self.window, ctx.pos0, ctx.lens, q.dtype)
+            return torch.bmm(p, kc[..., :C]).transpose(0, 1).contiguous()                              # [H,B,C]
+        Qb = min(self.query_block, S)
+        nblk = -(-S // Qb)
+        Sp, w = nblk * Qb, min(self.window, S)
+        span = Qb + w - 1
+        qp = F.pad(qcat, (0, 0, 0, 0, 0, Sp - S)).view(B * nblk, Qb * H, C + R)
+        kp = F.pad(rows, (0, 0, w - 1, Sp - S)).unfold(1, span, Qb)                                    # [B,nblk,C+R,span] view
+        kt = kp.reshape(B * nblk, C + R, span)
+        sc = seqmix.matmul_f32(qp, kt).view(B, nblk, Qb * H, span)
+        p = seqmix.window_softmax(sc, self.scale, False, H, Qb, nblk, w, self.window, ctx.pos0, ctx.lens, q.dtype)
+        o = torch.bmm(p.view(B * nblk, Qb * H, span), kt[:, :C].transpose(1, 2))                       # [B*nblk, Qb*H, C]
+        return o.view(B, Sp, H, C)[:, :S].permute(2, 0, 1, 3).reshape(H, B * S, C)

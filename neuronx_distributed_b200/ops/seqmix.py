@@ -198,6 +198,40 @@ def latent_window_attention(qa: torch.Tensor, q: torch.Tensor, off: int, keys: t
     return o.permute(2, 0, 1, 3).reshape(H, N, C).to(qa.dtype)
 
 
+def window_softmax(scores: torch.Tensor, scale: float, ring_mode: bool, H: int, Qb: int, nblk: int, w_eff: int, window: int,
+                   pos0: torch.Tensor, lens: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Softmax over the visible keys of float score rows made by block matrix products; masked entries come out as zeros.
+    Band mode: ``scores [B, nblk, Qb*H, span]``, column kk of block ``blk`` is position ``blk*Qb - (w_eff-1) + kk``; the query of
+    row ``(t, h)`` sits at ``i = blk*Qb + t`` and sees ``max(0, i-window+1) <= j <= i``; rows with ``i >= lens[b]`` are zeros.
+    Ring mode: ``scores [B, H, ring]`` of single tokens at ``pos0[b]``; ring row kk holds position ``p - ((p - kk) mod ring)``."""
+    if _cuda(scores):
+        _ext.count_launch()
+        return ext().window_softmax(scores, scale, ring_mode, H, Qb, nblk, w_eff, window, _i32(pos0), _i32(lens), out_dtype == torch.bfloat16)
+    span = scores.shape[-1]
+    kk = torch.arange(span)
+    if ring_mode:
+        p = pos0.long()[:, None]
+        m = torch.remainder(p - kk, span)
+        ok = ((p - m >= 0) & (m < window))[:, None, :] & (lens > 0)[:, None, None]                    # [B,1,ring]
+    else:
+        blk, t = torch.arange(nblk)[:, None, None], torch.arange(Qb)[None, :, None]
+        i, j = blk * Qb + t, blk * Qb - (w_eff - 1) + kk[None, None, :]                                # [nblk,Qb,1], [nblk,1,span]
+        ok = (j >= 0) & (j <= i) & (j > i - window)                                                   # [nblk,Qb,span]
+        ok = ok[None] & (i[None] < lens.long()[:, None, None, None])                                  # [B,nblk,Qb,span]
+        ok = ok[:, :, :, None, :].expand(-1, -1, -1, H, -1).reshape(scores.shape)
+    sc = (scores.float() * scale).masked_fill(~ok.expand(scores.shape), float("-inf"))
+    return torch.nan_to_num(torch.softmax(sc, -1), nan=0.0).to(out_dtype)
+
+
+def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Batched ``a @ b`` with a float result (float accumulation of bfloat16 operands is kept, not rounded)."""
+    if a.dtype == torch.float32:
+        return torch.bmm(a, b)
+    if a.is_cuda:
+        return torch.bmm(a, b, out_dtype=torch.float32)
+    return torch.bmm(a.float(), b.float())
+
+
 # -------------------------------------------------------------------------------------------------------------------- recurrences
 def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, zbias: torch.Tensor, tau: float, state: torch.Tensor,
              slots: torch.Tensor, lens: torch.Tensor, fresh: bool) -> torch.Tensor:
