@@ -11,7 +11,7 @@
 
 namespace seqmix {
 
-constexpr int kStage = 32;  // staged loads per thread and barrier
+constexpr int kStage = 28;  // staged loads per thread and barrier
 constexpr int kSteps = 8;   // tokens staged per barrier
 
 // Shared-memory image of one token: float4 {alpha, k, q, -} per key channel, then the slice's Vb values.
@@ -34,38 +34,57 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
         s[i] = (!fresh && live && d < D) ? sp[(long)d * V + j] : 0.f;
     }
     const long hq = (long)h * D, hv = (long)h * V + j0;
-    // element e of a chunk that starts at token t0: token t0 + e / per, field e % per
-    auto fetch = [&](int t0, int e) -> float {
-        const int t = t0 + e / per, f = e % per;
-        if (t >= len) return 0.f;
-        const long tok = (long)b * sb + (long)t * st;
-        if (f < 4 * D) {
-            const int d = f >> 2, w = f & 3;
-            if (w == 0) {
-                float zz = ldf(z + (long)b * z_sb + (long)t * z_st + hq + d) + zbias[hq + d];
-                return 1.f + expm1f(log_sigmoidf_(zz) * inv_tau);   // rounds once from an accurate value: no bias as alpha -> 1
+    // A chunk of TB tokens is fetched plane by plane (z, k, q: TB*D numbers each; v: TB*Vb), every load independent of the others and
+    // free of branches, so that all of a thread's loads are in flight together; tokens past the end read the last real token's
+    // numbers (never used).  The decays are formed when the chunk is written to shared memory.
+    const int nD = (TB * D + nthr - 1) / nthr, nV = (TB * Vb + nthr - 1) / nthr;     // loads per thread and plane (host keeps 3 nD + nV <= kStage)
+    const T* zp = z + (long)b * z_sb + hq;
+    const T* kp = k + (long)b * sb + hq;
+    const T* qp = q + (long)b * sb + hq;
+    const T* vp = v + (long)b * sb + hv;
+    float stage[kStage];
+    auto load_chunk = [&](int t0) {
+#pragma unroll
+        for (int x = 0; x < kStage; ++x) {
+            stage[x] = 0.f;
+            if (x < 3 * nD) {
+                const int pl = x / nD, idx = tid + (x - pl * nD) * nthr;
+                const int u = idx / D, d = idx - u * D, t = min(t0 + u, len - 1);
+                if (u < TB) stage[x] = pl == 0 ? ldf(zp + (long)t * z_st + d) : ldf((pl == 1 ? kp : qp) + (long)t * st + d);
+            } else if (x < 3 * nD + nV) {
+                const int idx = tid + (x - 3 * nD) * nthr;
+                const int u = idx / Vb, jj = idx - u * Vb, t = min(t0 + u, len - 1);
+                if (u < TB && j0 + jj < V) stage[x] = ldf(vp + (long)t * st + jj);
             }
-            if (w == 1) return ldf(k + tok + hq + d);
-            if (w == 2) return ldf(q + tok + hq + d) * qscale;
-            return 0.f;
         }
-        return (j0 + f - 4 * D < V) ? ldf(v + tok + hv + f - 4 * D) : 0.f;
     };
-    for (int e = tid; e < chunk; e += nthr) sm[e] = fetch(0, e);
+    auto store_chunk = [&](float* dst) {
+#pragma unroll
+        for (int x = 0; x < kStage; ++x) {
+            if (x < 3 * nD) {
+                const int pl = x / nD, idx = tid + (x - pl * nD) * nthr;
+                const int u = idx / D, d = idx - u * D;
+                if (u < TB) {
+                    float val = stage[x];
+                    if (pl == 0) val = 1.f + expm1f(log_sigmoidf_(val + zbias[hq + d]) * inv_tau);   // one rounding of an accurate value
+                    else if (pl == 2) val *= qscale;
+                    dst[u * per + 4 * d + pl] = val;
+                }
+            } else if (x < 3 * nD + nV) {
+                const int idx = tid + (x - 3 * nD) * nthr;
+                const int u = idx / Vb, jj = idx - u * Vb;
+                if (u < TB) dst[u * per + 4 * D + jj] = stage[x];
+            }
+        }
+    };
     const int nchunks = (len + TB - 1) / TB;
+    if (nchunks > 0) { load_chunk(0); store_chunk(sm); }
     for (int c = 0; c < nchunks; ++c) {
         const float* cur = sm + (c & 1) * chunk;
         float* nxt = sm + ((c + 1) & 1) * chunk;
         __syncthreads();
-        float stage[kStage];
         const bool more = c + 1 < nchunks;
-        if (more) {
-#pragma unroll
-            for (int x = 0; x < kStage; ++x) {
-                const int e = tid + x * nthr;
-                stage[x] = e < chunk ? fetch((c + 1) * TB, e) : 0.f;
-            }
-        }
+        if (more) load_chunk((c + 1) * TB);
         const int steps = min(TB, len - c * TB);
         for (int u = 0; u < steps; ++u) {
             const float* tokp = cur + u * per;
@@ -84,13 +103,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
             for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (r == 0 && live) out[(((long)b * S + c * TB + u) * H + h) * V + j] = acc;
         }
-        if (more) {
-#pragma unroll
-            for (int x = 0; x < kStage; ++x) {
-                const int e = tid + x * nthr;
-                if (e < chunk) nxt[e] = stage[x];
-            }
-        }
+        if (more) store_chunk(nxt);
     }
     if (r == 0 && live)
         for (int t = len; t < S; ++t) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
@@ -126,8 +139,11 @@ static bool gla_launch(const void* q, const void* k, const void* v, long sb, lon
     int threads = ((R * Vb + 31) / 32) * 32;
     const int per = 4 * D + ((Vb + 3) & ~3);
     int TB = S < kSteps ? (S < 1 ? 1 : S) : kSteps;
-    while (TB > 1 && ((long)TB * per > (long)kStage * threads || 2L * TB * per * 4 > 96 * 1024)) --TB;
-    if ((long)TB * per > (long)kStage * threads || 2L * TB * per * 4 > 96 * 1024) return false;
+    auto fits = [&](int tb) {
+        return 3 * ((tb * D + threads - 1) / threads) + (tb * Vb + threads - 1) / threads <= kStage && 2L * tb * per * 4 <= 96 * 1024;
+    };
+    while (TB > 1 && !fits(TB)) --TB;
+    if (!fits(TB)) return false;
     dim3 grid(H, B, (V + Vb - 1) / Vb);
     const size_t smem = 2 * (size_t)TB * per * sizeof(float);
 #define SEQMIX_GLA(P)                                                                                                             \

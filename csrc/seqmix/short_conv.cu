@@ -62,9 +62,102 @@ __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_s
     }
 }
 
+// Vector form (taps <= 8, channels and strides multiples of 4, 16-byte aligned): a thread owns 4 channels and a run of 8 consecutive
+// tokens, keeps the previous taps-1 inputs in registers and reads every input once.  A block covers 128 channels x 64 tokens; only
+// the block of the first 64 tokens can touch the carried history, and it replaces it after its own reads.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(c), __high2float(c));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), c = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&c);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+constexpr int kVecTaps = 8, kRun = 8;
+
+template <typename Tin, typename Tout>
+__global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long x_st, const float* __restrict__ w,
+                                      const float* __restrict__ bias, Tin* state, const int* __restrict__ slots,
+                                      const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual,
+                                      Tout* __restrict__ out) {
+    const int c = (blockIdx.x * 32 + threadIdx.x) * 4, b = blockIdx.z, tbase = blockIdx.y * (kRun * 8) + threadIdx.y * kRun;
+    const int len = min(lens[b], S), hist = taps - 1;
+    Tin* st = state + (long)slots[b] * hist * C;
+    const Tin* xb = x + (long)b * x_sb;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto in4 = [&](int s) -> float4 {
+        if (s >= 0) return ld4(xb + (long)s * x_st + c);
+        if (!fresh) return ld4(st + (long)(hist + s) * C + c);
+        return zero;
+    };
+    if (c < C) {
+        float4 wr[kVecTaps], prev[kVecTaps - 1];          // right-aligned: wr[kVecTaps-1] weighs the current token
+#pragma unroll
+        for (int k = 0; k < kVecTaps; ++k) {
+            const int j = k - (kVecTaps - taps);
+            wr[k] = j >= 0 ? make_float4(w[(long)c * taps + j], w[(long)(c + 1) * taps + j], w[(long)(c + 2) * taps + j], w[(long)(c + 3) * taps + j]) : zero;
+        }
+        const float4 bc = bias ? ld4(bias + c) : zero;
+#pragma unroll
+        for (int k = 0; k < kVecTaps - 1; ++k) {
+            const int s = tbase - (kVecTaps - 1) + k;
+            prev[k] = (k >= kVecTaps - 1 - hist && tbase < len) ? in4(s) : zero;
+        }
+#pragma unroll
+        for (int tt = 0; tt < kRun; ++tt) {
+            const int t = tbase + tt;
+            if (t < S) {
+                float4 acc = zero, cur = zero;
+                if (t < len) {
+                    cur = ld4(xb + (long)t * x_st + c);
+                    acc = bc;
+#pragma unroll
+                    for (int k = 0; k < kVecTaps - 1; ++k) {
+                        acc.x = fmaf(wr[k].x, prev[k].x, acc.x); acc.y = fmaf(wr[k].y, prev[k].y, acc.y);
+                        acc.z = fmaf(wr[k].z, prev[k].z, acc.z); acc.w = fmaf(wr[k].w, prev[k].w, acc.w);
+                    }
+                    const float4 wl = wr[kVecTaps - 1];
+                    acc.x = fmaf(wl.x, cur.x, acc.x); acc.y = fmaf(wl.y, cur.y, acc.y);
+                    acc.z = fmaf(wl.z, cur.z, acc.z); acc.w = fmaf(wl.w, cur.w, acc.w);
+                    if (residual) { acc.x += cur.x; acc.y += cur.y; acc.z += cur.z; acc.w += cur.w; }
+                }
+                st4(out + ((long)b * S + t) * C + c, acc);
+#pragma unroll
+                for (int k = 0; k < kVecTaps - 2; ++k) prev[k] = prev[k + 1];
+                prev[kVecTaps - 2] = cur;
+            }
+        }
+    }
+    if (blockIdx.y != 0) return;
+    __syncthreads();   // every read of the old history is done before it is replaced
+    if (threadIdx.y == 0 && c < C && hist > 0) {
+        float4 nh[kVecTaps - 1];
+#pragma unroll
+        for (int i = 0; i < kVecTaps - 1; ++i) nh[i] = i < hist ? in4(len - hist + i) : zero;
+#pragma unroll
+        for (int i = 0; i < kVecTaps - 1; ++i)
+            if (i < hist) st4(st + (long)i * C + c, nh[i]);
+    }
+}
+
 template <typename Tin, typename Tout>
 static void launch(const void* x, long x_sb, long x_st, const float* w, const float* bias, void* state, const int* slots,
                    const int* lens, int B, int S, int C, int taps, int fresh, int residual, void* out, cudaStream_t s) {
+    const bool vec = taps <= kVecTaps && C % 4 == 0 && x_sb % 4 == 0 && x_st % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                     (uintptr_t)state % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0);
+    if (vec) {
+        dim3 grid((C / 4 + 31) / 32, (S + kRun * 8 - 1) / (kRun * 8), B), block(32, 8);
+        short_conv_vec_kernel<Tin, Tout><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
+                                                               fresh, residual, (Tout*)out);
+        return;
+    }
     int ty = S >= 16 ? 16 : (S >= 4 ? 4 : 1);
     dim3 grid((C + 31) / 32, B), block(32, ty);
     short_conv_kernel<Tin, Tout><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
