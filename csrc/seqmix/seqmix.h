@@ -20,6 +20,14 @@ void window_softmax(const float* scores, long rows, int span, float scale, int r
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
               const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int S,
               int H, int D, int V, float* out, cudaStream_t s);
+// Chunked form of gla_scan for long runs of tokens (gla_chunked.cu): blk = (b * H + h) * chunks + c indexes Qe, Ke, Bc [blk, C, D],
+// G [blk, D], Vf [blk, C, V], A [blk, C, C] with C = gla_chunk_tokens(); Sl [blk, D, V] = Ke^T Vf goes through gla_carry.
+int gla_chunk_tokens();
+void gla_chunk_prep(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
+                    const float* zbias, float inv_tau, float qscale, const int* lens, int B, int S, int H, int D, int V, int chunks,
+                    float* Qe, float* Ke, float* Bc, float* G, float* Vf, float* A, cudaStream_t s);
+void gla_carry(float* Sl, const float* G, float* state, const int* slots, int fresh, int B, int chunks, int H, int D, int V,
+               cudaStream_t s);
 void rglru_scan(const void* u, int bf, const float* gr, const float* gi, int wb, const float* rbias, const float* ibias,
                 const float* lam_sp, const void* y, long y_sb, long y_st, float* state, const int* slots, const int* lens, int fresh,
                 int B, int S, int W, void* out, cudaStream_t s);

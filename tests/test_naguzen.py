@@ -209,6 +209,45 @@ def test_routed_ffn(device, rows, top, shared):
     assert torch.allclose(m(h.to(device)).cpu().double(), want, atol=2e-5)
 
 
+def _gla_plain(q, k, v, z, zb, tau, s0):
+    """Token by token in float64: S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t / sqrt(D), from the state s0 [H,D,V]."""
+    S, H, D = q.shape
+    alpha = torch.sigmoid(z.double() + zb.double()).pow(1.0 / tau).reshape(S, H, D)
+    st, out = s0.double().clone(), []
+    for t in range(S):
+        st = alpha[t][:, :, None] * st + k[t].double()[:, :, None] * v[t].double()[:, None, :]
+        out.append(torch.einsum("hdv,hd->hv", st, q[t].double()) * D ** -0.5)
+    return torch.stack(out), st
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,D,V,tau,bias", [(2, 20, 12, 7.0, 2.0), (1, 40, 72, 0.5, -6.0), (3, 33, 5, 64.0, 5.0)])
+def test_gla_scan_rows_of_many_lengths_and_a_carried_state(device, H, D, V, tau, bias):
+    """Rows that end just before, at and just after the edges of the 64-token chunks of the long-run form, one single token, decays
+    from almost 1 down to almost 0 (2^-17 per token and channel: nothing may overflow), states carried in from slots in use."""
+    g = torch.Generator().manual_seed(D)
+    lens = [63, 64, 65, 130, 1, 129, 200]
+    B, S = len(lens), max(lens)
+    p = torch.randn(B, S, H * (2 * D + V), generator=g)                      # one projection's output, as the layer makes it
+    cut = lambda t: (t[..., :H * D].unflatten(-1, (H, D)), t[..., H * D:2 * H * D].unflatten(-1, (H, D)), t[..., 2 * H * D:].unflatten(-1, (H, V)))
+    q, k, v = cut(p)
+    z, zb = torch.randn(B, S, H * D, generator=g) * 2, torch.randn(H * D, generator=g) + bias
+    slots = torch.tensor([6, 0, 3, 8, 2, 5, 1], dtype=torch.int32)
+    for fresh in (True, False):
+        state = torch.randn(9, H, D, V, generator=g)
+        st = state.clone().to(device)
+        dv = lambda t: t.to(device)
+        out = seqmix.gla_scan(*cut(dv(p)), dv(z), dv(zb), tau, st, dv(slots), dv(torch.tensor(lens, dtype=torch.int32)), fresh).cpu()
+        for b, n in enumerate(lens):
+            s0 = torch.zeros(H, D, V) if fresh else state[slots[b]]
+            want, last = _gla_plain(q[b, :n], k[b, :n], v[b, :n], z[b, :n], zb, tau, s0)
+            scale = want.abs().max()
+            assert (out[b, :n].double() - want).abs().max() < 2e-5 * scale, (b, n, fresh)
+            assert (out[b, n:] == 0).all()
+            assert (st[slots[b]].cpu().double() - last).abs().max() < 2e-5 * max(1.0, last.abs().max()), (b, n, fresh)
+        assert torch.equal(st[4].cpu(), state[4]) and torch.equal(st[7].cpu(), state[7])          # slots of no row are not touched
+
+
 SINGLE = {"attention": [attn_spec()], "attention_wide_window": [attn_spec(window=64, heads=1, dim=8, rot=4, vdim=8, kv_rank=100, q_rank=16)],
           "gla": [gla_spec()], "gla_one_head": [gla_spec(heads=1, dim=40, vdim=72, tau=1.0)], "rglru": [lru_spec()],
           "rglru_one_block": [lru_spec(width=40, blocks=1, conv=1)], "dense": [gla_spec(mlp=DENSE)], "moe": [lru_spec(mlp=moe())]}
