@@ -114,12 +114,22 @@ __global__ void gla_carry_kernel(float* __restrict__ Sl, const float* __restrict
     const long bh = (long)b * H + h;
     float* sp = state + ((long)slots[b] * H + h) * D * V + e;
     float run = fresh ? 0.f : *sp;
-#pragma unroll 4
-    for (int c = 0; c < nC; ++c) {
-        const long o = (bh * nC + c) * D * V + e;
-        const float loc = Sl[o];
-        Sl[o] = run;
-        run = fmaf(G[(bh * nC + c) * D + d], run, loc);
+    constexpr int kU = 8;                                      // chunks whose loads are in flight together
+    for (int c0 = 0; c0 < nC; c0 += kU) {
+        float loc[kU], gg[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int c = min(c0 + u, nC - 1);
+            loc[u] = __ldcs(Sl + (bh * nC + c) * D * V + e);
+            gg[u] = G[(bh * nC + c) * D + d];
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            if (c0 + u < nC) {
+                __stcs(Sl + (bh * nC + c0 + u) * D * V + e, run);
+                run = fmaf(gg[u], run, loc[u]);
+            }
+        }
     }
     *sp = run;
 }

@@ -2,11 +2,14 @@
 
 Per token the layer keeps only a normalised latent ``c`` (``kv_rank`` numbers) and ONE rotated key part shared by all heads
 (``rot_dim`` numbers).  Queries go through their own latent.  A head's score against position j is
-``(q_unrot . W_uk c_j + q_rot . k_rot_j) * scale``; it is evaluated in the absorbed form ``(W_uk^T q_unrot) . c_j`` so that
-neither keys nor values are ever expanded: the attention kernel returns the weighted sum of latents and ``W_uv`` is applied
-afterwards.  Position i sees ``i - window < j <= i``, so the cache is a ring of ``window`` rows per sequence
-(``csrc/seqmix/latent_attention.cu``).  A prompt that starts a sequence attends over its own prepared rows and leaves its last
-``window`` rows in the ring; later single tokens append to the ring and attend over it."""
+``(q_unrot . W_uk c_j + q_rot . k_rot_j) * scale``.  Position i sees ``i - window < j <= i``, so the cache is a ring of ``window``
+rows per sequence (``csrc/seqmix/latent_attention.cu``).  A prompt that starts a sequence attends over its own prepared rows
+and leaves its last ``window`` rows in the ring; later single tokens append to the ring and attend over it.
+
+Two evaluation orders.  Single tokens are bound by reading the ring, so they use the absorbed form ``(W_uk^T q_unrot) . c_j``:
+neither keys nor values are expanded, the weighted sum of latents comes back and ``W_uv`` is applied afterwards.  Prompts are
+bound by arithmetic, so they expand every head's keys and values once and spend ``dim + rot_dim + vdim`` multiply-adds per
+(query, key, head) instead of ``2 kv_rank + rot_dim``.  With ``block_products=False`` both run the one-kernel absorbed form."""
 from __future__ import annotations
 
 from typing import Dict, Tuple
@@ -48,9 +51,11 @@ class LatentWindowAttention(nn.Module):
         rows = seqmix.latent_kv_store(kv, self.dkv_norm, self.eps, self.inv_freq, self.rot_dims, ctx.pos0, ctx.lens, ctx.slots, st["kv"],
                                       want_rows=ctx.fresh)
         seqmix.rope_q_(q, D, self.rot_dims, self.inv_freq, ctx.pos0)
+        if ctx.fresh and self.block_products:
+            return F.linear(self._attend_prompt(q, rows, ctx), self.o).view(B, S, -1)
         qa = torch.bmm(q.view(N, H, D + R)[:, :, :D].transpose(0, 1), self.uk)                       # [H,N,D] @ [H,D,C]
-        if self.block_products:
-            o = self._attend_products(qa, q, rows, ctx, st)
+        if self.block_products and S == 1:
+            o = self._attend_ring(qa, q, ctx, st)
         elif ctx.fresh:
             o = seqmix.latent_window_attention(qa, q, D, rows, None, ctx.pos0, ctx.lens, self.window, self.scale)
         else:
@@ -58,27 +63,49 @@ class LatentWindowAttention(nn.Module):
         ov = torch.bmm(o, self.uv.transpose(1, 2))                                                     # [H,N,C] @ [H,C,V]
         return F.linear(ov.transpose(0, 1).reshape(N, H * self.vdim), self.o).view(B, S, -1)
 
-    def _attend_products(self, qa: torch.Tensor, q: torch.Tensor, rows, ctx, st) -> torch.Tensor:
-        """Scores and weighted sums as matrix products with the heads folded into the row dimension (all heads share the keys):
-        a prompt is cut into blocks of ``query_block`` tokens, each multiplied with the ``query_block + window - 1`` key rows it can
-        see; a single token multiplies its sequence's ring.  The softmax over the visible keys runs in float in between
-        (``window_softmax``).  Returns ``[H, N, C]``."""
+    def _attend_prompt(self, q: torch.Tensor, rows: torch.Tensor, ctx) -> torch.Tensor:
+        """A prompt in the expanded form: every head's keys ``[W_uk c | rotated part]`` and values ``W_uv c`` are formed by two
+        matrix products, which costs ``dim + rot_dim + vdim`` multiply-adds per (query, key, head) instead of the absorbed form's
+        ``2 kv_rank + rot_dim``.  Queries, keys and values are laid out ``(sequence, head)``-major with the tokens padded to whole
+        blocks of ``query_block``; block ``m`` of that layout multiplies the ``query_block + window - 1`` rows that end with its
+        own, taken as an overlapping strided view, so one batched product covers all sequences, heads and blocks.  Rows of the view
+        that belong to the neighbouring head (before a sequence's first token) are positions < 0, which the softmax masks.
+        Returns the heads' outputs ``[B*S, H*vdim]``."""
         B, S, H, _ = q.shape
-        C, R, D = self.kv_rank, self.rot_dim, self.dim
-        qcat = torch.cat([qa.view(H, B, S, C).permute(1, 2, 0, 3), q[..., D:]], -1)                   # [B,S,H,C+R]
-        if not ctx.fresh:
-            kc = st["kv"].index_select(0, ctx.slots.long())                                            # [B,ring,C+R]
-            sc = seqmix.matmul_f32(qcat.view(B, H, C + R), kc.transpose(1, 2))                         # [B,H,ring]
-            p = seqmix.window_softmax(sc, self.scale, True, H, 1, 1, 1, self.window, ctx.pos0, ctx.lens, q.dtype)
-            return torch.bmm(p, kc[..., :C]).transpose(0, 1).contiguous()                              # [H,B,C]
+        C, R, D, V = self.kv_rank, self.rot_dim, self.dim, self.vdim
         Qb = min(self.query_block, S)
         nblk = -(-S // Qb)
         Sp, w = nblk * Qb, min(self.window, S)
-        span = Qb + w - 1
-        qp = F.pad(qcat, (0, 0, 0, 0, 0, Sp - S)).view(B * nblk, Qb * H, C + R)
-        kp = F.pad(rows, (0, 0, w - 1, Sp - S)).unfold(1, span, Qb)                                    # [B,nblk,C+R,span] view
-        kt = kp.reshape(B * nblk, C + R, span)
-        sc = seqmix.matmul_f32(qp, kt).view(B, nblk, Qb * H, span)
-        p = seqmix.window_softmax(sc, self.scale, False, H, Qb, nblk, w, self.window, ctx.pos0, ctx.lens, q.dtype)
-        o = torch.bmm(p.view(B * nblk, Qb * H, span), kt[:, :C].transpose(1, 2))                       # [B*nblk, Qb*H, C]
-        return o.view(B, Sp, H, C)[:, :S].permute(2, 0, 1, 3).reshape(H, B * S, C)
+        span, pad, M = Qb + w - 1, w - 1, B * H * nblk
+        c = rows[..., :C]
+        kbuf, vbuf = rows.new_zeros(pad + B * H * Sp, D + R), rows.new_zeros(pad + B * H * Sp, V)
+        kv, vv = kbuf[pad:].view(B, H, Sp, D + R), vbuf[pad:].view(B, H, Sp, V)
+        kv[:, :, :S, :D] = F.linear(c, self.uk.view(H * D, C)).view(B, S, H, D).permute(0, 2, 1, 3)
+        kv[:, :, :S, D:] = rows[:, None, :, C:]
+        vv[:, :, :S] = F.linear(c, self.uv.view(H * V, C)).view(B, S, H, V).permute(0, 2, 1, 3)
+        qbuf = q.new_zeros(B, H, Sp, D + R) if Sp != S else q.new_empty(B, H, Sp, D + R)
+        qbuf[:, :, :S] = q.permute(0, 2, 1, 3)
+        qm = qbuf.view(M, Qb, D + R)
+        kwin = kbuf.as_strided((M, span, D + R), (Qb * (D + R), D + R, 1))
+        vwin = vbuf.as_strided((M, span, V), (Qb * V, V, 1))
+        pos0, lens = ctx.pos0.repeat_interleave(H), ctx.lens.repeat_interleave(H)
+        out = q.new_empty(M, Qb, V)
+        group = max(1, (1 << 28) // (nblk * Qb * span))                      # (sequence, head) pairs per pass: scores stay <= 1 GiB
+        for g0 in range(0, B * H, group):
+            g1 = min(B * H, g0 + group)
+            m0, m1 = g0 * nblk, g1 * nblk
+            sc = seqmix.matmul_f32(qm[m0:m1], kwin[m0:m1].transpose(1, 2)).view(g1 - g0, nblk, Qb, span)
+            p = seqmix.window_softmax(sc, self.scale, False, 1, Qb, nblk, w, self.window, pos0[g0:g1], lens[g0:g1], q.dtype)
+            torch.bmm(p.view(m1 - m0, Qb, span), vwin[m0:m1], out=out[m0:m1])
+        return out.view(B, H, Sp, V)[:, :, :S].permute(0, 2, 1, 3).reshape(B * S, H * V)
+
+    def _attend_ring(self, qa: torch.Tensor, q: torch.Tensor, ctx, st) -> torch.Tensor:
+        """Single tokens against their sequences' rings, in the absorbed form, as matrix products with the heads folded into the
+        row dimension (all heads share the keys); the softmax over the visible ring rows runs in float in between.  ``[H, B, C]``."""
+        B, S, H, _ = q.shape
+        C, R, D = self.kv_rank, self.rot_dim, self.dim
+        qcat = torch.cat([qa.view(H, B, S, C).permute(1, 2, 0, 3), q[..., D:]], -1)                   # [B,1,H,C+R]
+        kc = st["kv"].index_select(0, ctx.slots.long())                                                # [B,ring,C+R]
+        sc = seqmix.matmul_f32(qcat.view(B, H, C + R), kc.transpose(1, 2))                             # [B,H,ring]
+        p = seqmix.window_softmax(sc, self.scale, True, H, 1, 1, 1, self.window, ctx.pos0, ctx.lens, q.dtype)
+        return torch.bmm(p, kc[..., :C]).transpose(0, 1).contiguous()                                  # [H,B,C]

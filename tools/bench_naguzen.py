@@ -185,25 +185,36 @@ def kernel_table(dev, steps, warmup):
     ql = rnd(B, S, H, 128)
     cos, sin = ops.rope.rope_tables(S, 128, 10000.0, dev)
     add("llama apply_rotary [B,S,16,128]", lambda: ops.rope.apply_rotary(ql, cos, sin), N * H * 128 * 4, like="rope_q_ / latent_kv_store")
-    qa, keys = rnd(H, N, C), rnd(B, S, C + R)
+    from neuronx_distributed_b200.models.naguzen import StepContext
+    from neuronx_distributed_b200.modules.attention.latent_attention import LatentWindowAttention
+
+    Vd = 128
+    att = LatentWindowAttention(W, H, D, R, Vd, C, 1536, window=win, scale=0.07, rot_base=10000.0, rot_dims=R, eps=1e-6, dtype=bf, device=dev)
+    with torch.no_grad():
+        att.uk.normal_(0.0, 0.04), att.uv.normal_(0.0, 0.04)
+    keys = rnd(B, S, C + R)
     pairs = B * H * sum(min(p + 1, win) for p in range(S))
-    add("latent_window_attention prompt (window 1024)", lambda: seqmix.latent_window_attention(qa, q, D, keys, None, pos0, lens, win, 0.07),
-        flops=pairs * (2 * (C + R) + 2 * C))
+    ctx = StepContext(lens, slots, pos0, True)
+    add("latent attention prompt (expand keys / values, block products, window softmax; window 1024)",
+        lambda: att._attend_prompt(q, keys, ctx), flops=pairs * 2 * (D + R + Vd) + 2 * N * C * H * (D + Vd))
     qf, kf, vf = rnd(B, S, H, 128), rnd(B, S, 4, 128), rnd(B, S, 4, 128)
     add("llama flash_attention prompt (causal, full)", lambda: ops.attention.flash_attention(qf, kf, vf, causal=True),
-        flops=4 * B * H * 128 * S * (S + 1) / 2, like="latent_window_attention prompt")
+        flops=4 * B * H * 128 * S * (S + 1) / 2, like="latent attention prompt")
     Bd = 8
     qa1, q1 = rnd(H, Bd, C), rnd(Bd, 1, H, D + R)
     cache8 = rnd(Bd, win, C + R)
     l1, s8, p8 = torch.ones(Bd, dtype=i32, device=dev), torch.arange(Bd, dtype=i32, device=dev), torch.full((Bd,), 2047, dtype=i32, device=dev)
-    add("latent_window_attention decode (8 rows, ring 1024)", lambda: seqmix.latent_window_attention(qa1, q1, D, cache8, s8, p8, l1, win, 0.07),
-        bytes_=Bd * win * (C + R) * 2)
+    ctx1 = StepContext(l1, s8, p8, False)
+    add("latent attention decode (8 rows, ring 1024: gather, scores, ring softmax, weighted latents)",
+        lambda: att._attend_ring(qa1, q1, ctx1, {"kv": cache8}), bytes_=Bd * win * (C + R) * 2)
+    add("latent_window_attention one-kernel form, decode (8 rows, ring 1024)",
+        lambda: seqmix.latent_window_attention(qa1, q1, D, cache8, s8, p8, l1, win, 0.07), bytes_=Bd * win * (C + R) * 2)
     e = ops._ext.ext()
     if e is not None and hasattr(e, "decode_attention"):
         qd, kc, vc = rnd(Bd, 1, H, 128), rnd(Bd, 2048, 4, 128), rnd(Bd, 2048, 4, 128)
         pl = torch.full((Bd,), 2047, dtype=torch.long, device=dev)
         add("llama decode_attention (8 rows, 2048 keys, 4 KV heads)", lambda: e.decode_attention(qd, kc, vc, pl, 1.0 / math.sqrt(128)),
-            bytes_=Bd * 2048 * 4 * 128 * 4, like="latent_window_attention decode")
+            bytes_=Bd * 2048 * 4 * 128 * 4, like="latent attention decode")
     # recurrences
     Hg, Dg, Vg = 4, 256, 512
     p = rnd(B, S, 2 * Hg * Dg + Hg * Vg)
