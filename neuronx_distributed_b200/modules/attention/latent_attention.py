@@ -68,7 +68,7 @@ class LatentWindowAttention(nn.Module):
         matrix products, which costs ``dim + rot_dim + vdim`` multiply-adds per (query, key, head) instead of the absorbed form's
         ``2 kv_rank + rot_dim``.  Queries, keys and values are laid out ``(sequence, head)``-major with the tokens padded to whole
         blocks of ``query_block``; block ``m`` of that layout multiplies the ``query_block + window - 1`` rows that end with its
-        own, taken as an overlapping strided view, so one batched product covers all sequences, heads and blocks.  Rows of the view
+        own (rounded up to whole 128-byte score rows), taken as an overlapping strided view, so one batched product covers all sequences, heads and blocks.  Rows of the view
         that belong to the neighbouring head (before a sequence's first token) are positions < 0, which the softmax masks.
         Returns the heads' outputs ``[B*S, H*vdim]``."""
         B, S, H, _ = q.shape
@@ -76,10 +76,12 @@ class LatentWindowAttention(nn.Module):
         Qb = min(self.query_block, S)
         nblk = -(-S // Qb)
         Sp, w = nblk * Qb, min(self.window, S)
-        span, pad, M = Qb + w - 1, w - 1, B * H * nblk
+        pad, M = w - 1, B * H * nblk
+        span = -(-(Qb + w - 1) // 32) * 32            # whole 128-byte rows of scores; the extra columns are positions after the query
+        tail = span - (Qb + w - 1)
         c = rows[..., :C]
-        kbuf, vbuf = rows.new_zeros(pad + B * H * Sp, D + R), rows.new_zeros(pad + B * H * Sp, V)
-        kv, vv = kbuf[pad:].view(B, H, Sp, D + R), vbuf[pad:].view(B, H, Sp, V)
+        kbuf, vbuf = rows.new_zeros(pad + B * H * Sp + tail, D + R), rows.new_zeros(pad + B * H * Sp + tail, V)
+        kv, vv = kbuf[pad:pad + B * H * Sp].view(B, H, Sp, D + R), vbuf[pad:pad + B * H * Sp].view(B, H, Sp, V)
         kv[:, :, :S, :D] = F.linear(c, self.uk.view(H * D, C)).view(B, S, H, D).permute(0, 2, 1, 3)
         kv[:, :, :S, D:] = rows[:, None, :, C:]
         vv[:, :, :S] = F.linear(c, self.uv.view(H * V, C)).view(B, S, H, V).permute(0, 2, 1, 3)
