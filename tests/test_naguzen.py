@@ -514,6 +514,27 @@ def test_trace_runner_command_line(mixed, tmp_path):
     close(got, torch.stack([oracle.forward(full, w, reqs["a"])[0][10], oracle.forward(full, w, reqs["b"])[0][4]]), TOL32)
 
 
+def test_generate_command_line(mixed, tmp_path):
+    """Greedy generation of an unequal batch through the command line (registry, static batch, sampler) equals the oracle's; a
+    sampled run with a fixed seed repeats itself and stays inside the vocabulary."""
+    cfg, w, _, _, _ = mixed
+    path = _save_model_dir(str(tmp_path / "model"), cfg, w)
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    prompts = [tokens_for(cfg, 7, 41), tokens_for(cfg, 3, 42)]
+    cmd = [os.path.join(ROOT, "bin", "generate"), "--model", path, "--dtype", "float32", "--max-new-tokens", "5"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    env = {**os.environ, "CUDA_VISIBLE_DEVICES": ""}
+    run = lambda extra: subprocess.run(cmd + extra, capture_output=True, text=True, timeout=600, env=env)
+    r = run([])
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [[int(t) for t in line.split(",")] for line in r.stdout.strip().splitlines()[-2:]]
+    assert got == [_oracle_greedy(full, w, p, 5) for p in prompts]
+    a, b = run(["--do-sample", "--top-k", "8", "--temperature", "0.7", "--seed", "3"]), run(["--do-sample", "--top-k", "8", "--temperature", "0.7", "--seed", "3"])
+    assert a.returncode == 0 and a.stdout == b.stdout, a.stderr[-2000:]
+    assert all(0 <= int(t) < cfg["vocab"] for line in a.stdout.strip().splitlines()[-2:] for t in line.split(","))
+
+
 @pytest.mark.gpu
 def test_bfloat16_serving_close_to_the_oracle():
     """The serving precision: bfloat16 matrix products, float statistics / states / residual.  Prompt + decode, against float64.
