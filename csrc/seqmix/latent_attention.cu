@@ -64,6 +64,77 @@ __global__ void rope_q_kernel(T* __restrict__ q, long q_sn, long q_sh, int N, in
     stf(x + i + half, v * cs + u * sn);
 }
 
+// Vector forms of the two kernels above (every extent, stride and offset a multiple of four elements, 16-byte aligned bases): a
+// lane handles four consecutive coordinates per step and keeps the latent in registers between the statistic and the scaling.
+constexpr int kStoreVec = 8;        // float4 per lane: latents up to 1024 numbers
+
+template <typename T>
+__global__ void latent_kv_store_vec_kernel(const T* __restrict__ kv, long kv_sb, long kv_st, int B, int S, int C, int R, int dims,
+                                           const float* __restrict__ nw, float eps, const float* __restrict__ inv_freq,
+                                           const int* __restrict__ pos0, const int* __restrict__ lens, const int* __restrict__ slots,
+                                           T* __restrict__ cache, int ring, T* __restrict__ rows) {
+    const int n = blockIdx.x * blockDim.y + threadIdx.y, lane = threadIdx.x;
+    if (n >= B * S) return;
+    const int b = n / S, t = n % S, len = min(lens[b], S);
+    if (t >= len) return;
+    const int p = pos0[b] + t, CR = C + R, half = dims / 2;
+    const T* x = kv + (long)b * kv_sb + (long)t * kv_st;
+    T* dst_row = rows ? rows + (long)n * CR : nullptr;
+    T* dst_cache = (cache && t >= len - ring) ? cache + ((long)slots[b] * ring + (p % ring)) * CR : nullptr;
+    float4 v[kStoreVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < kStoreVec; ++e) {
+        const int c = (e * 32 + lane) * 4;
+        v[e] = c < C ? ld4(x + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[e].x, v[e].x, fmaf(v[e].y, v[e].y, fmaf(v[e].z, v[e].z, fmaf(v[e].w, v[e].w, ss))));
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)C + eps);
+#pragma unroll
+    for (int e = 0; e < kStoreVec; ++e) {
+        const int c = (e * 32 + lane) * 4;
+        if (c < C) {
+            const float4 g = ld4(nw + c);
+            const float4 o = make_float4(v[e].x * inv * g.x, v[e].y * inv * g.y, v[e].z * inv * g.z, v[e].w * inv * g.w);
+            if (dst_row) st4(dst_row + c, o);
+            if (dst_cache) st4(dst_cache + c, o);
+        }
+    }
+    for (int i = lane * 4; i < half; i += 128) {
+        const float4 u = ld4(x + C + i), w = ld4(x + C + i + half), f = ld4(inv_freq + i);
+        float4 sn, cs;
+        sincosf((float)p * f.x, &sn.x, &cs.x); sincosf((float)p * f.y, &sn.y, &cs.y);
+        sincosf((float)p * f.z, &sn.z, &cs.z); sincosf((float)p * f.w, &sn.w, &cs.w);
+        const float4 a = make_float4(u.x * cs.x - w.x * sn.x, u.y * cs.y - w.y * sn.y, u.z * cs.z - w.z * sn.z, u.w * cs.w - w.w * sn.w);
+        const float4 bb = make_float4(w.x * cs.x + u.x * sn.x, w.y * cs.y + u.y * sn.y, w.z * cs.z + u.z * sn.z, w.w * cs.w + u.w * sn.w);
+        if (dst_row) { st4(dst_row + C + i, a); st4(dst_row + C + i + half, bb); }
+        if (dst_cache) { st4(dst_cache + C + i, a); st4(dst_cache + C + i + half, bb); }
+    }
+    for (int i = dims + lane; i < R; i += 32) {      // coordinates past the rotated ones pass unchanged
+        float u = ldf(x + C + i);
+        if (dst_row) stf(dst_row + C + i, u);
+        if (dst_cache) stf(dst_cache + C + i, u);
+    }
+}
+
+template <typename T>
+__global__ void rope_q_vec_kernel(T* __restrict__ q, long q_sn, long q_sh, int N, int S, int H, int dims,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ pos0) {
+    const int quads = dims / 8;                      // groups of four pairs per head
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)N * H * quads) return;
+    const int i = (int)(idx % quads) * 4, h = (idx / quads) % H, n = idx / ((long)quads * H), half = dims / 2;
+    const int p = pos0[n / S] + n % S;
+    T* x = q + (long)n * q_sn + (long)h * q_sh;
+    const float4 u = ld4(x + i), w = ld4(x + i + half), f = ld4(inv_freq + i);
+    float4 sn, cs;
+    sincosf((float)p * f.x, &sn.x, &cs.x); sincosf((float)p * f.y, &sn.y, &cs.y);
+    sincosf((float)p * f.z, &sn.z, &cs.z); sincosf((float)p * f.w, &sn.w, &cs.w);
+    st4(x + i, make_float4(u.x * cs.x - w.x * sn.x, u.y * cs.y - w.y * sn.y, u.z * cs.z - w.z * sn.z, u.w * cs.w - w.w * sn.w));
+    st4(x + i + half, make_float4(w.x * cs.x + u.x * sn.x, w.y * cs.y + u.y * sn.y, w.z * cs.z + u.z * sn.z, w.w * cs.w + u.w * sn.w));
+}
+
 template <typename T, int MAXE>
 __global__ void latent_window_attn_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, const T* __restrict__ qr, long qr_sn,
                                           long qr_sh, const T* __restrict__ keys, long key_sb, int ring,
@@ -170,6 +241,17 @@ void latent_kv_store(const void* kv, int bf, long kv_sb, long kv_st, int B, int 
                      const float* inv_freq, const int* pos0, const int* lens, const int* slots, void* cache, int ring, void* rows,
                      cudaStream_t s) {
     dim3 block(32, 8), grid((B * S + 7) / 8);
+    const size_t es = bf ? 2 : 4;
+    auto al = [&](const void* p) { return p == nullptr || (uintptr_t)p % (4 * es) == 0; };
+    const bool vec = C % 4 == 0 && R % 4 == 0 && dims % 8 == 0 && C <= kStoreVec * 128 && kv_sb % 4 == 0 && kv_st % 4 == 0 && al(kv) &&
+                     al(cache) && al(rows) && (uintptr_t)nw % 16 == 0 && (uintptr_t)inv_freq % 16 == 0;
+    if (vec) {
+        if (bf) latent_kv_store_vec_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)kv, kv_sb, kv_st, B, S, C, R, dims, nw, eps, inv_freq,
+                                                                       pos0, lens, slots, (bf16*)cache, ring, (bf16*)rows);
+        else latent_kv_store_vec_kernel<float><<<grid, block, 0, s>>>((const float*)kv, kv_sb, kv_st, B, S, C, R, dims, nw, eps, inv_freq,
+                                                                      pos0, lens, slots, (float*)cache, ring, (float*)rows);
+        return;
+    }
     if (bf) latent_kv_store_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)kv, kv_sb, kv_st, B, S, C, R, dims, nw, eps, inv_freq, pos0,
                                                                lens, slots, (bf16*)cache, ring, (bf16*)rows);
     else latent_kv_store_kernel<float><<<grid, block, 0, s>>>((const float*)kv, kv_sb, kv_st, B, S, C, R, dims, nw, eps, inv_freq, pos0,
@@ -180,6 +262,13 @@ void rope_q(void* q, int bf, long q_sn, long q_sh, int N, int S, int H, int dims
     const long total = (long)N * H * (dims / 2);
     if (total == 0) return;
     const int threads = 256;
+    const size_t es = bf ? 2 : 4;
+    if (dims % 8 == 0 && q_sn % 4 == 0 && q_sh % 4 == 0 && (uintptr_t)q % (4 * es) == 0 && (uintptr_t)inv_freq % 16 == 0) {
+        const unsigned vblocks = (unsigned)((total / 4 + threads - 1) / threads);
+        if (bf) rope_q_vec_kernel<bf16><<<vblocks, threads, 0, s>>>((bf16*)q, q_sn, q_sh, N, S, H, dims, inv_freq, pos0);
+        else rope_q_vec_kernel<float><<<vblocks, threads, 0, s>>>((float*)q, q_sn, q_sh, N, S, H, dims, inv_freq, pos0);
+        return;
+    }
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (bf) rope_q_kernel<bf16><<<blocks, threads, 0, s>>>((bf16*)q, q_sn, q_sh, N, S, H, dims, inv_freq, pos0);
     else rope_q_kernel<float><<<blocks, threads, 0, s>>>((float*)q, q_sn, q_sh, N, S, H, dims, inv_freq, pos0);

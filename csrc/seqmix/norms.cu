@@ -1,23 +1,60 @@
 // RMS norms of the sequence-mixer models: y = x / sqrt(mean(x^2) + eps) * w with w a vector or ONE number for all coordinates,
 // optionally times silu(gate), written out or accumulated into a float residual stream (x_res += norm(y): the residual sum of a
-// layer that normalises the sublayer's OUTPUT).  One warp per row; statistics in float.
+// layer that normalises the sublayer's OUTPUT).  Statistics in float.
 #include "seq_common.cuh"
 #include "seqmix.h"
 
 namespace seqmix {
 
-template <typename Tin, typename Tout>
+// blockDim.x threads share a row (32: a warp per row, many rows; 256: a block per row, few rows such as single-token steps),
+// blockDim.y rows per block.  VEC: four consecutive coordinates per thread and access (extents, strides and bases multiples of four
+// elements, the gain a vector with stride 1 or one number).
+template <typename Tin, typename Tout, bool VEC>
 __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int rows, int C, const float* __restrict__ w, int w_stride,
                                 float eps, const Tout* __restrict__ gate, long gate_stride, Tout* __restrict__ out, long out_stride,
                                 float* res, long res_stride) {
-    const int row = blockIdx.x * blockDim.y + threadIdx.y, lane = threadIdx.x;
-    if (row >= rows) return;
-    const Tin* xr = x + (long)row * x_stride;
+    __shared__ float part[8];
+    const int row = blockIdx.x * blockDim.y + threadIdx.y, tx = threadIdx.x, TX = blockDim.x;
+    const bool on = row < rows;
+    const Tin* xr = x + (long)(on ? row : 0) * x_stride;
     float ss = 0.f;
-    for (int c = lane; c < C; c += 32) { float v = ldf(xr + c); ss = fmaf(v, v, ss); }
+    if (on) {
+        if (VEC) {
+            for (int c = tx * 4; c < C; c += TX * 4) {
+                const float4 v = ld4(xr + c);
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+        } else {
+            for (int c = tx; c < C; c += TX) { float v = ldf(xr + c); ss = fmaf(v, v, ss); }
+        }
+    }
     ss = warp_sum(ss);
+    if (TX > 32) {                              // one row per block: fold the warps' sums
+        if ((tx & 31) == 0) part[tx >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int k = 0; k < TX / 32; ++k) ss += part[k];
+    }
+    if (!on) return;
     const float inv = 1.f / sqrtf(ss / (float)C + eps);
-    for (int c = lane; c < C; c += 32) {
+    if (VEC) {
+        for (int c = tx * 4; c < C; c += TX * 4) {
+            float4 v = ld4(xr + c);
+            const float4 g = w_stride ? ld4(w + c) : make_float4(w[0], w[0], w[0], w[0]);
+            v = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+            if (gate) {
+                const float4 t = ld4(gate + (long)row * gate_stride + c);
+                v.x *= t.x * sigmoidf_(t.x); v.y *= t.y * sigmoidf_(t.y); v.z *= t.z * sigmoidf_(t.z); v.w *= t.w * sigmoidf_(t.w);
+            }
+            if (res) {
+                float* r = res + (long)row * res_stride + c;
+                const float4 o = ld4(r);
+                st4(r, make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w));
+            } else st4(out + (long)row * out_stride + c, v);
+        }
+        return;
+    }
+    for (int c = tx; c < C; c += TX) {
         float v = ldf(xr + c) * inv * w[(long)c * w_stride];
         if (gate) { float g = ldf(gate + (long)row * gate_stride + c); v *= g * sigmoidf_(g); }
         if (res) res[(long)row * res_stride + c] += v;
@@ -27,14 +64,21 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int ro
 
 void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const float* w, int w_stride, float eps, const void* gate,
               long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, cudaStream_t s) {
-    dim3 block(32, 8), grid((rows + 7) / 8);
-#define SEQMIX_NORM(TI, TO)                                                                                                      \
-    rms_norm_kernel<TI, TO><<<grid, block, 0, s>>>((const TI*)x, x_stride, rows, C, w, w_stride, eps, (const TO*)gate, gate_stride, \
-                                                   (TO*)out, out_stride, res, res_stride)
+    const bool few = rows < 148 * 8 && C >= 512;
+    dim3 block(few ? 256 : 32, few ? 1 : 8), grid(few ? rows : (rows + 7) / 8);
+    const size_t ei = in_bf16 ? 2 : 4, eo = out_bf16 ? 2 : 4;
+    auto al = [](const void* p, size_t e) { return p == nullptr || (uintptr_t)p % (4 * e) == 0; };
+    const bool vec = C % 4 == 0 && x_stride % 4 == 0 && (w_stride == 0 || w_stride == 1) && al(x, ei) && al(w, 4) && al(gate, eo) &&
+                     (!gate || gate_stride % 4 == 0) && al(out, eo) && (res || out_stride % 4 == 0) && al(res, 4) && (!res || res_stride % 4 == 0);
+#define SEQMIX_NORM_V(TI, TO, V)                                                                                                    \
+    rms_norm_kernel<TI, TO, V><<<grid, block, 0, s>>>((const TI*)x, x_stride, rows, C, w, w_stride, eps, (const TO*)gate, gate_stride, \
+                                                      (TO*)out, out_stride, res, res_stride)
+#define SEQMIX_NORM(TI, TO) do { if (vec) SEQMIX_NORM_V(TI, TO, true); else SEQMIX_NORM_V(TI, TO, false); } while (0)
     if (in_bf16 && out_bf16) SEQMIX_NORM(bf16, bf16);
     else if (!in_bf16 && out_bf16) SEQMIX_NORM(float, bf16);
     else if (!in_bf16 && !out_bf16) SEQMIX_NORM(float, float);
     else SEQMIX_NORM(bf16, float);
+#undef SEQMIX_NORM_V
 #undef SEQMIX_NORM
 }
 

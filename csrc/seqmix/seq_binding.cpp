@@ -112,6 +112,17 @@ Tensor latent_window_attention(const Tensor& qa, const Tensor& q, int64_t off, c
     TORCH_CHECK(qa.scalar_type() == q.scalar_type() && q.scalar_type() == keys.scalar_type(), "dtype mismatch");
     Tensor out = at::empty({H, N, C}, qa.options());
     const char* qr = (const char*)q.data_ptr() + off * q.element_size();
+    if (S == 1 && seqmix::latent_ring_decode_fits(C, R)) {      // single tokens: split over the ring, partial softmaxes merged
+        const long ns = seqmix::latent_ring_decode_splits((int)keys.size(1));
+        const auto f = qa.options().dtype(at::kFloat);
+        Tensor pm = at::empty({B, ns, H}, f), pl = at::empty({B, ns, H}, f), pa = at::empty({B, ns, H, C}, f);
+        seqmix::latent_ring_decode(qa.data_ptr(), is_bf(qa), C, (long)N * C, qr, (long)H * Dq, Dq, keys.data_ptr(), keys.stride(0),
+                                   (int)keys.size(1), key_index ? i32(*key_index) : nullptr, i32(pos0), i32(lens), B, H, C, R, (int)window,
+                                   (float)scale, pm.data_ptr<float>(), pl.data_ptr<float>(), pa.data_ptr<float>(), out.data_ptr(), C,
+                                   (long)N * C, stream());
+        check_launch();
+        return out;
+    }
     seqmix::latent_window_attention(qa.data_ptr(), is_bf(qa), C, (long)N * C, qr, (long)H * Dq, Dq, keys.data_ptr(), keys.stride(0),
                                     (int)keys.size(1), key_index ? i32(*key_index) : nullptr, i32(pos0), i32(lens), B, S, H, C, R,
                                     (int)window, (float)scale, out.data_ptr(), C, (long)N * C, stream());

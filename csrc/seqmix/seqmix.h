@@ -15,6 +15,14 @@ void rope_q(void* q, int bf, long q_sn, long q_sh, int N, int S, int H, int dims
 void latent_window_attention(const void* qa, int bf, long qa_sn, long qa_sh, const void* qr, long qr_sn, long qr_sh, const void* keys,
                              long key_sb, int ring, const int* key_index, const int* pos0, const int* lens, int B, int S, int H, int C,
                              int R, int window, float scale, void* out, long out_sn, long out_sh, cudaStream_t s);
+// Single new tokens against their rings (latent_decode.cu): blocks over (ring chunk, sequence, head tile) leave partial softmaxes
+// part_m / part_l [B, splits, H] and part_acc [B, splits, H, C] (float), which a second kernel merges into out[h, b, :].
+int latent_ring_decode_splits(int ring);
+bool latent_ring_decode_fits(int C, int R);
+void latent_ring_decode(const void* qa, int bf, long qa_sn, long qa_sh, const void* qr, long qr_sn, long qr_sh, const void* keys,
+                        long key_sb, int ring, const int* key_index, const int* pos0, const int* lens, int B, int H, int C, int R,
+                        int window, float scale, float* part_m, float* part_l, float* part_acc, void* out, long out_sn, long out_sh,
+                        cudaStream_t s);
 void window_softmax(const float* scores, long rows, int span, float scale, int ring_mode, int H, int Qb, int nblk, int w_eff, int window,
                     const int* pos0, const int* lens, void* out, int out_bf16, cudaStream_t s);
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,

@@ -65,21 +65,6 @@ __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_s
 // Vector form (taps <= 8, channels and strides multiples of 4, 16-byte aligned): a thread owns 4 channels and a run of 8 consecutive
 // tokens, keeps the previous taps-1 inputs in registers and reads every input once.  A block covers 128 channels x 64 tokens; only
 // the block of the first 64 tokens can touch the carried history, and it replaces it after its own reads.
-__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 ld4(const bf16* p) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    return make_float4(__low2float(a), __high2float(a), __low2float(c), __high2float(c));
-}
-__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void st4(bf16* p, float4 v) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), c = __floats2bfloat162_rn(v.z, v.w);
-    uint2 raw;
-    raw.x = *reinterpret_cast<unsigned*>(&a);
-    raw.y = *reinterpret_cast<unsigned*>(&c);
-    *reinterpret_cast<uint2*>(p) = raw;
-}
-
 constexpr int kVecTaps = 8, kRun = 8;
 
 template <typename Tin, typename Tout>
@@ -110,13 +95,16 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
             const int s = tbase - (kVecTaps - 1) + k;
             prev[k] = (k >= kVecTaps - 1 - hist && tbase < len) ? in4(s) : zero;
         }
+        float4 run[kRun];                                 // the run's own inputs, all loads in flight together
+#pragma unroll
+        for (int tt = 0; tt < kRun; ++tt) run[tt] = tbase + tt < len ? ld4(xb + (long)(tbase + tt) * x_st + c) : zero;
 #pragma unroll
         for (int tt = 0; tt < kRun; ++tt) {
             const int t = tbase + tt;
             if (t < S) {
-                float4 acc = zero, cur = zero;
+                float4 acc = zero;
+                const float4 cur = run[tt];
                 if (t < len) {
-                    cur = ld4(xb + (long)t * x_st + c);
                     acc = bc;
 #pragma unroll
                     for (int k = 0; k < kVecTaps - 1; ++k) {

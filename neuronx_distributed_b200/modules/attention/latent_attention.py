@@ -7,7 +7,9 @@ rows per sequence (``csrc/seqmix/latent_attention.cu``).  A prompt that starts a
 and leaves its last ``window`` rows in the ring; later single tokens append to the ring and attend over it.
 
 Two evaluation orders.  Single tokens are bound by reading the ring, so they use the absorbed form ``(W_uk^T q_unrot) . c_j``:
-neither keys nor values are expanded, the weighted sum of latents comes back and ``W_uv`` is applied afterwards.  Prompts are
+neither keys nor values are expanded, the weighted sum of latents comes back and ``W_uv`` is applied afterwards; one kernel
+per ring chunk scores all heads against the chunk's rows and weights the same rows, a second merges the chunks' partial softmaxes
+(``csrc/seqmix/latent_decode.cu``; rows wider than the kernel's limit go through matrix products over the gathered ring).  Prompts are
 bound by arithmetic, so they expand every head's keys and values once and spend ``dim + rot_dim + vdim`` multiply-adds per
 (query, key, head) instead of ``2 kv_rank + rot_dim``.  With ``block_products=False`` both run the one-kernel absorbed form."""
 from __future__ import annotations
@@ -54,7 +56,9 @@ class LatentWindowAttention(nn.Module):
         if ctx.fresh and self.block_products:
             return F.linear(self._attend_prompt(q, rows, ctx), self.o).view(B, S, -1)
         qa = torch.bmm(q.view(N, H, D + R)[:, :, :D].transpose(0, 1), self.uk)                       # [H,N,D] @ [H,D,C]
-        if self.block_products and S == 1:
+        if S == 1 and not ctx.fresh and self.kv_rank + R <= seqmix.LATENT_ROW_MAX:
+            o = seqmix.latent_window_attention(qa, q, D, st["kv"], ctx.slots, ctx.pos0, ctx.lens, self.window, self.scale)
+        elif self.block_products and S == 1:
             o = self._attend_ring(qa, q, ctx, st)
         elif ctx.fresh:
             o = seqmix.latent_window_attention(qa, q, D, rows, None, ctx.pos0, ctx.lens, self.window, self.scale)

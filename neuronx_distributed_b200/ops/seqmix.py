@@ -173,6 +173,9 @@ def rope_q_(q: torch.Tensor, off: int, dims: int, inv_freq: torch.Tensor, pos0: 
     return q
 
 
+LATENT_ROW_MAX = 640        # widest key-store row (latent + rotated part) the attention kernels take
+
+
 def latent_window_attention(qa: torch.Tensor, q: torch.Tensor, off: int, keys: torch.Tensor, key_index: Optional[torch.Tensor],
                             pos0: torch.Tensor, lens: torch.Tensor, window: int, scale: float) -> torch.Tensor:
     """``qa [H, B*S, C]`` absorbed queries, ``q [B,S,H,Dq]`` whose coordinates from ``off`` are the rotated part, ``keys

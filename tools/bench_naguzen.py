@@ -205,10 +205,10 @@ def kernel_table(dev, steps, warmup):
     cache8 = rnd(Bd, win, C + R)
     l1, s8, p8 = torch.ones(Bd, dtype=i32, device=dev), torch.arange(Bd, dtype=i32, device=dev), torch.full((Bd,), 2047, dtype=i32, device=dev)
     ctx1 = StepContext(l1, s8, p8, False)
-    add("latent attention decode (8 rows, ring 1024: gather, scores, ring softmax, weighted latents)",
-        lambda: att._attend_ring(qa1, q1, ctx1, {"kv": cache8}), bytes_=Bd * win * (C + R) * 2)
-    add("latent_window_attention one-kernel form, decode (8 rows, ring 1024)",
+    add("latent attention decode (8 rows, ring 1024: ring-chunk partial softmaxes + merge, 2 kernels)",
         lambda: seqmix.latent_window_attention(qa1, q1, D, cache8, s8, p8, l1, win, 0.07), bytes_=Bd * win * (C + R) * 2)
+    add("latent attention decode as matrix products (gather, scores, ring softmax, weighted latents)",
+        lambda: att._attend_ring(qa1, q1, ctx1, {"kv": cache8}), bytes_=Bd * win * (C + R) * 2)
     e = ops._ext.ext()
     if e is not None and hasattr(e, "decode_attention"):
         qd, kc, vc = rnd(Bd, 1, H, 128), rnd(Bd, 2048, 4, 128), rnd(Bd, 2048, 4, 128)
