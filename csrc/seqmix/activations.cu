@@ -43,7 +43,7 @@ static void act_launch(const void* x, void* out, long n, float ap, float an, cud
     act_kernel<T, ACT><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const T*)x, (T*)out, n, n16, ap, an);
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restrict__ sel, const T* __restrict__ x, long x_stride,
                                     int M, int O, int I, int act, T* __restrict__ out) {
     const int o = blockIdx.x * blockDim.y + threadIdx.y, m = blockIdx.y, lane = threadIdx.x;
@@ -51,7 +51,22 @@ __global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restri
     const T* wr = w + ((long)sel[m] * O + o) * I;
     const T* xr = x + (long)m * x_stride;
     float acc = 0.f;
-    for (int i = lane; i < I; i += 32) acc = fmaf(ldf(wr + i), ldf(xr + i), acc);
+    if (VEC) {                                   // four weights per lane and access, two accesses in flight
+        float acc2 = 0.f;
+        int i = lane * 4;
+        for (; i + 128 < I; i += 256) {
+            const float4 a = ld4(wr + i), b = ld4(wr + i + 128), xa = ld4(xr + i), xb = ld4(xr + i + 128);
+            acc = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, acc))));
+            acc2 = fmaf(b.x, xb.x, fmaf(b.y, xb.y, fmaf(b.z, xb.z, fmaf(b.w, xb.w, acc2))));
+        }
+        if (i < I) {
+            const float4 a = ld4(wr + i), xa = ld4(xr + i);
+            acc = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, acc))));
+        }
+        acc += acc2;
+    } else {
+        for (int i = lane; i < I; i += 32) acc = fmaf(ldf(wr + i), ldf(xr + i), acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) stf(out + (long)m * O + o, act ? gelu_erf_(acc) : acc);
 }
@@ -80,8 +95,12 @@ void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_s
                   cudaStream_t s) {
     if (M == 0) return;
     dim3 block(32, 8), grid((O + 7) / 8, M);
-    if (bf) indexed_gemv_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)w, sel, (const bf16*)x, x_stride, M, O, I, act, (bf16*)out);
-    else indexed_gemv_kernel<float><<<grid, block, 0, s>>>((const float*)w, sel, (const float*)x, x_stride, M, O, I, act, (float*)out);
+    const size_t a4 = bf ? 8 : 16;
+    const bool vec = I % 4 == 0 && x_stride % 4 == 0 && (uintptr_t)w % a4 == 0 && (uintptr_t)x % a4 == 0;
+#define SEQMIX_IGEMV(T, V) indexed_gemv_kernel<T, V><<<grid, block, 0, s>>>((const T*)w, sel, (const T*)x, x_stride, M, O, I, act, (T*)out)
+    if (bf) { if (vec) SEQMIX_IGEMV(bf16, true); else SEQMIX_IGEMV(bf16, false); }
+    else { if (vec) SEQMIX_IGEMV(float, true); else SEQMIX_IGEMV(float, false); }
+#undef SEQMIX_IGEMV
 }
 
 void moe_combine(const void* rows, const int* src, const float* weight, const void* base, int bf, int N, int top, int C, void* out,

@@ -164,6 +164,82 @@ bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long
               : gla_launch<float>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, state, slots, lens, fresh, B, S, H, D, V, out, s);
 }
 
+// One new token per sequence (token generation): the step is bound by reading and writing the state once, so a block owns 64
+// consecutive value columns of one (sequence, head) and all key channels; thread (column, group g of 4) walks the rows d = g, g+4, ...
+// with whole 256-byte rows per access and eight independent rows in flight; the four groups' sums meet in shared memory.
+constexpr int kStepCols = 64, kStepGroups = 4, kStepUnroll = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kStepCols* kStepGroups)
+gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long sb, const T* __restrict__ z, long z_sb,
+                const float* __restrict__ zbias, float inv_tau, float qscale, float* state, const int* __restrict__ slots,
+                const int* __restrict__ lens, int fresh, int H, int D, int V, float* __restrict__ out) {
+    extern __shared__ float sm[];              // alpha [D], k [D], q [D], sums [groups][cols]
+    float *sa = sm, *sk = sm + D, *sq = sm + 2 * D, *red = sm + 3 * D;
+    const int h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, jl = tid % kStepCols, g = tid / kStepCols;
+    const int j = blockIdx.x * kStepCols + jl;
+    const bool live = j < V;
+    float* o = out + ((long)b * H + h) * V + j;
+    if (lens[b] < 1) {                          // a padded row: zeros out, state untouched
+        if (g == 0 && live) *o = 0.f;
+        return;
+    }
+    const long hq = (long)h * D;
+    for (int d = tid; d < D; d += kStepCols * kStepGroups) {
+        sa[d] = 1.f + expm1f(log_sigmoidf_(ldf(z + (long)b * z_sb + hq + d) + zbias[hq + d]) * inv_tau);
+        sk[d] = ldf(k + (long)b * sb + hq + d);
+        sq[d] = ldf(q + (long)b * sb + hq + d) * qscale;
+    }
+    __syncthreads();
+    const float vj = live ? ldf(v + (long)b * sb + (long)h * V + j) : 0.f;
+    float* sp = state + (((long)slots[b] * H + h) * D) * V + j;
+    float acc = 0.f;
+    for (int d0 = g; d0 < D; d0 += kStepGroups * kStepUnroll) {
+        float s[kStepUnroll];
+#pragma unroll
+        for (int u = 0; u < kStepUnroll; ++u) {
+            const int d = d0 + u * kStepGroups;
+            s[u] = (!fresh && live && d < D) ? sp[(long)d * V] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kStepUnroll; ++u) {
+            const int d = d0 + u * kStepGroups;
+            if (d < D) {
+                s[u] = fmaf(sa[d], s[u], sk[d] * vj);
+                acc = fmaf(s[u], sq[d], acc);
+                if (live) sp[(long)d * V] = s[u];
+            }
+        }
+    }
+    red[g * kStepCols + jl] = acc;
+    __syncthreads();
+    if (g == 0 && live) {
+        float t = 0.f;
+#pragma unroll
+        for (int x = 0; x < kStepGroups; ++x) t += red[x * kStepCols + jl];
+        *o = t;
+    }
+}
+
+template <typename T>
+static void gla_step_launch(const void* q, const void* k, const void* v, long sb, const void* z, long z_sb, const float* zbias,
+                            float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D,
+                            int V, float* out, cudaStream_t s) {
+    dim3 grid((V + kStepCols - 1) / kStepCols, H, B);
+    const size_t smem = (size_t)(3 * D + kStepGroups * kStepCols) * sizeof(float);
+    gla_step_kernel<T><<<grid, kStepCols * kStepGroups, smem, s>>>((const T*)q, (const T*)k, (const T*)v, sb, (const T*)z, z_sb, zbias, inv_tau,
+                                                                  qscale, state, slots, lens, fresh, H, D, V, out);
+}
+
+bool gla_step(const void* q, const void* k, const void* v, int bf, long sb, const void* z, long z_sb, const float* zbias, float inv_tau,
+              float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D, int V, float* out,
+              cudaStream_t s) {
+    if ((size_t)(3 * D + kStepGroups * kStepCols) * sizeof(float) > 48 * 1024) return false;
+    if (bf) gla_step_launch<bf16>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, state, slots, lens, fresh, B, H, D, V, out, s);
+    else gla_step_launch<float>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, state, slots, lens, fresh, B, H, D, V, out, s);
+    return true;
+}
+
 // One block = 32 channels of one sequence x TY time lanes.  Each lane scans its slice of the tokens from zero keeping the product of
 // its decays; the carries are folded through shared memory; the lanes scan again from their true carry and write the outputs.
 template <typename T>

@@ -203,6 +203,12 @@ Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() && q.scalar_type() == z.scalar_type(), "dtype mismatch");
     if (S >= kGlaChunkedFrom) return gla_scan_chunked(q, k, v, z, zbias, tau, state, slots, lens, fresh);
     Tensor out = at::empty({B, S, H, V}, q.options().dtype(at::kFloat));
+    if (S == 1 && seqmix::gla_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), is_bf(q), q.stride(0), z.data_ptr(), z.stride(0), f32(zbias),
+                                   (float)(1.0 / tau), (float)(1.0 / std::sqrt((double)D)), state.data_ptr<float>(), i32(slots), i32(lens),
+                                   fresh, B, H, D, V, out.data_ptr<float>(), stream())) {
+        check_launch();
+        return out;
+    }
     bool ok = seqmix::gla_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), is_bf(q), q.stride(0), q.stride(1), z.data_ptr(), z.stride(0),
                                z.stride(1), f32(zbias), (float)(1.0 / tau), (float)(1.0 / std::sqrt((double)D)), state.data_ptr<float>(),
                                i32(slots), i32(lens), fresh, B, S, H, D, V, out.data_ptr<float>(), stream());

@@ -28,6 +28,10 @@ void window_softmax(const float* scores, long rows, int span, float scale, int r
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
               const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int S,
               int H, int D, int V, float* out, cudaStream_t s);
+// One token per sequence (S == 1): a block per 64 value columns of a (sequence, head); false when the key size does not fit.
+bool gla_step(const void* q, const void* k, const void* v, int bf, long sb, const void* z, long z_sb, const float* zbias, float inv_tau,
+              float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D, int V, float* out,
+              cudaStream_t s);
 // Chunked form of gla_scan for long runs of tokens (gla_chunked.cu): blk = (b * H + h) * chunks + c indexes Qe, Ke, Bc [blk, C, D],
 // G [blk, D], Vf [blk, C, V], A [blk, C, C] with C = gla_chunk_tokens(); Sl [blk, D, V] = Ke^T Vf goes through gla_carry.
 int gla_chunk_tokens();

@@ -5,7 +5,10 @@ gating, kept as stacks ``[E, ff, width]`` / ``[E, width, ff]``.
 
 Two execution shapes, both summing the chosen experts in float (``moe_combine``):
 * few rows (token generation): the chosen experts' matrices are streamed once by ``indexed_gemv`` — no host synchronisation;
-* many rows (prompts): rows are sorted by expert and every non-empty expert runs two dense matrix products."""
+* many rows (prompts), bfloat16 with sizes the tensor-core kernel takes: the framework's blockwise layout (``blockwise.py``: rows
+  grouped by expert into blocks of 128, one index-build launch) and its grouped tcgen05 GEMM, two launches for all experts;
+* many rows otherwise (float, odd sizes, extension not built): rows are sorted by expert and every non-empty expert runs two
+  dense matrix products."""
 from __future__ import annotations
 
 from typing import Callable, Optional
@@ -38,6 +41,38 @@ class RoutedFFN(nn.Module):
         w, idx = torch.topk(scores, self.top, dim=-1)
         return w * self.weight_scale, idx
 
+    block_rows = 128               # rows per block of the grouped GEMM
+
+    def _grouped_kernels(self, h: torch.Tensor):
+        """The main extension when its grouped GEMM can take this call (bfloat16 on the GPU, sizes in whole 64s), else None."""
+        if not (h.is_cuda and h.dtype == torch.bfloat16 and self.width % 64 == 0 and self.ff % 64 == 0):
+            return None
+        from ...ops import _ext
+
+        e = _ext.ext()
+        return e if e is not None and hasattr(e, "grouped_gemm") else None
+
+    def _experts_grouped(self, h: torch.Tensor, idx: torch.Tensor):
+        """All chosen experts in two grouped GEMMs over the blockwise layout → (rows ``[blocks * 128, width]``, ``src [N, top]``
+        naming the row that holds each (token, choice)).  Padding slots compute on token 0 and are never referenced."""
+        from ...ops import _ext
+        from .blockwise import build_block_metadata
+
+        e, bs = _ext.ext(), self.block_rows
+        b2e, tp2id, _ = build_block_metadata(idx, self.experts, bs)
+        b2e = b2e.to(torch.int32).contiguous()
+        tp = tp2id[: b2e.numel() * bs].long()
+        x = h[tp.clamp(min=0)]
+        _ext.count_launch(2)
+        eo = e.grouped_gemm(seqmix.gelu_erf(e.grouped_gemm(x, self.up, b2e, bs, True)), self.down, b2e, bs, True)
+        N, top = idx.shape                                                         # no host synchronisation: padding slots write
+        tok, exp = tp.clamp(min=0), b2e.long().repeat_interleave(bs)               # to a spare entry past the end
+        choice = (idx[tok] == exp[:, None]).to(torch.int32).argmax(1)
+        flat = torch.empty(N * top + 1, dtype=torch.int32, device=h.device)
+        flat[torch.where(tp >= 0, tok * top + choice, N * top)] = torch.arange(tp.numel(), dtype=torch.int32, device=h.device)
+        src = flat[: N * top].view(N, top)
+        return eo, src
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """``h [N, width]`` → ``[N, width]``."""
         N = h.shape[0]
@@ -48,6 +83,8 @@ class RoutedFFN(nn.Module):
             mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), True)
             eo = seqmix.indexed_gemv(self.down, sel, mid, False)
             src = torch.arange(M, device=h.device, dtype=torch.int32).view(N, self.top)
+        elif self._grouped_kernels(h) is not None:
+            eo, src = self._experts_grouped(h, idx)
         else:
             flat = idx.reshape(-1)
             order = torch.argsort(flat, stable=True)

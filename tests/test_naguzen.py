@@ -209,6 +209,36 @@ def test_routed_ffn(device, rows, top, shared):
     assert torch.allclose(m(h.to(device)).cpu().double(), want, atol=2e-5)
 
 
+def test_routed_ffn_blockwise_layout(monkeypatch):
+    """The blockwise grouped path's bookkeeping (rows grouped by expert into padded blocks, and which row holds each (token, choice))
+    with a stand-in for the grouped GEMM kernel: same result as the oracle, also when some experts get no rows."""
+    import types
+
+    from neuronx_distributed_b200.ops import _ext
+
+    def grouped_gemm(x, w, b2e, block_rows, trans_b):
+        assert trans_b and x.shape[0] == b2e.numel() * block_rows
+        return torch.einsum("bti,boi->bto", x.view(b2e.numel(), block_rows, -1), w[b2e.long()]).reshape(x.shape[0], -1)
+
+    fake = types.SimpleNamespace(grouped_gemm=grouped_gemm)
+    monkeypatch.setattr(_ext, "_PLAN_PROXY", fake)
+    for rows, experts, top in [(70, 6, 3), (33, 9, 1), (300, 4, 2)]:
+        f = moe(experts=experts, top=top, scale=0.6, ff=24, shared=40)
+        cfg = make_cfg([gla_spec(mlp=f)])
+        P = oracle.sub(random_checkpoint(cfg, seed=rows), "l0.mlp.")
+        m = RoutedFFN(cfg["width"], 24, experts, top, weight_scale=0.6, shared_ff=40, dtype=torch.float32)
+        m.block_rows = 16
+        m._grouped_kernels = lambda h: fake
+        with torch.no_grad():
+            m.up.copy_(torch.stack([P[f"e{e}.up"] for e in range(experts)]))
+            m.down.copy_(torch.stack([P[f"e{e}.down"] for e in range(experts)]))
+            m.router.linear_router.weight.copy_(P["router"])
+            m.shared_up.copy_(P["shared.up"]), m.shared_down.copy_(P["shared.down"])
+        h = torch.randn(rows, cfg["width"], generator=torch.Generator().manual_seed(5))
+        want = oracle.moe_ff(h.double(), {k: v.double() for k, v in P.items()}, f)
+        assert torch.allclose(m(h).double(), want, atol=2e-5)
+
+
 def _gla_plain(q, k, v, z, zb, tau, s0):
     """Token by token in float64: S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t / sqrt(D), from the state s0 [H,D,V]."""
     S, H, D = q.shape
@@ -550,13 +580,15 @@ def test_bfloat16_serving_close_to_the_oracle():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows", [6, 90])
-def test_bfloat16_routed_ffn_rows_with_a_clear_choice(rows):
-    f = moe(experts=6, top=2, scale=1.7, ff=24, shared=40)
-    cfg = make_cfg([gla_spec(mlp=f)])
+@pytest.mark.parametrize("rows,width,ff", [(6, 48, 24), (90, 48, 24), (90, 128, 64), (700, 64, 192)])
+def test_bfloat16_routed_ffn_rows_with_a_clear_choice(rows, width, ff):
+    """Few rows (streamed experts), many rows of odd sizes (an expert at a time) and many rows in whole 64s (the blockwise grouped
+    GEMM, when the main extension is built) against the oracle, on the rows whose choice of experts is not a close call."""
+    f = moe(experts=6, top=2, scale=1.7, ff=ff, shared=40)
+    cfg = make_cfg([gla_spec(mlp=f)], width=width)
     w = random_checkpoint(cfg, seed=4)
     P = oracle.sub(w, "l0.mlp.")
-    m = RoutedFFN(cfg["width"], 24, 6, 2, weight_scale=1.7, shared_ff=40, dtype=torch.bfloat16, device="cuda")
+    m = RoutedFFN(cfg["width"], ff, 6, 2, weight_scale=1.7, shared_ff=40, dtype=torch.bfloat16, device="cuda")
     with torch.no_grad():
         m.up.copy_(torch.stack([P[f"e{e}.up"] for e in range(6)])), m.down.copy_(torch.stack([P[f"e{e}.down"] for e in range(6)]))
         m.router.linear_router.weight.copy_(P["router"])
