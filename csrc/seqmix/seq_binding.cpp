@@ -130,6 +130,27 @@ Tensor latent_window_attention(const Tensor& qa, const Tensor& q, int64_t off, c
     return out;
 }
 
+bool latent_prompt_attention_fits(int64_t D, int64_t R, int64_t CR, int64_t VD) {
+    return seqmix::latent_prompt_attention_fits((int)D, (int)R, (int)CR, (int)VD);
+}
+
+// q [B,S,H,D+R], kx [B,S,H*D], rows [B,S,CR], v [B,S,H*VD] (all bfloat16, contiguous) → [B*S, H*VD]
+Tensor latent_prompt_attention(const Tensor& q, const Tensor& kx, const Tensor& rows, const Tensor& v, const Tensor& lens, int64_t D,
+                               int64_t R, int64_t VD, int64_t window, double scale) {
+    TORCH_CHECK(q.is_cuda() && q.dim() == 4 && q.is_contiguous() && kx.is_contiguous() && rows.is_contiguous() && v.is_contiguous() &&
+                    rows.dim() == 3, "bad prompt attention operands");
+    TORCH_CHECK(is_bf(q) && is_bf(kx) && is_bf(rows) && is_bf(v), "the fused prompt attention takes bfloat16");
+    const int B = q.size(0), S = q.size(1), H = q.size(2), CR = rows.size(2);
+    TORCH_CHECK(q.size(3) == D + R && kx.numel() == (long)B * S * H * D && v.numel() == (long)B * S * H * VD && rows.size(0) == B &&
+                    rows.size(1) == S && CR >= R, "shape mismatch");
+    Tensor out = at::empty({(long)B * S, (long)H * VD}, q.options());
+    bool ok = seqmix::latent_prompt_attention(q.data_ptr(), kx.data_ptr(), rows.data_ptr(), v.data_ptr(), i32(lens), B, S, H, (int)D, (int)R,
+                                              CR, (int)VD, (int)window, (float)scale, out.data_ptr(), stream());
+    TORCH_CHECK(ok, "latent_prompt_attention: sizes do not fit the kernel");
+    check_launch();
+    return out;
+}
+
 // scores float [..., span] (contiguous) → softmax over the visible keys, in `out_bf16`'s dtype.  Band mode: rows (b, block, t, head);
 // ring mode: rows (b, head) of single tokens at positions pos0.
 Tensor window_softmax(const Tensor& scores, double scale, bool ring_mode, int64_t H, int64_t Qb, int64_t nblk, int64_t w_eff, int64_t window,
@@ -277,6 +298,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("rope_q_", &rope_q_);
     m.def("latent_window_attention", &latent_window_attention);
     m.def("window_softmax", &window_softmax);
+    m.def("latent_prompt_attention", &latent_prompt_attention);
+    m.def("latent_prompt_attention_fits", &latent_prompt_attention_fits);
     m.def("gla_scan", &gla_scan);
     m.def("rglru_scan", &rglru_scan);
     m.def("xielu", &xielu);

@@ -23,6 +23,11 @@ void latent_ring_decode(const void* qa, int bf, long qa_sn, long qa_sh, const vo
                         long key_sb, int ring, const int* key_index, const int* pos0, const int* lens, int B, int H, int C, int R,
                         int window, float scale, float* part_m, float* part_l, float* part_acc, void* out, long out_sn, long out_sh,
                         cudaStream_t s);
+// Prompt attention in the expanded form as one fused kernel (latent_prefill.cu; bfloat16, sizes in whole 16s up to 256): q [B,S,H,D+R],
+// kx [B,S,H,D], rows [B,S,CR] (last R numbers: the shared rotated key part), v [B,S,H,VD] → out [B,S,H*VD].  false: sizes do not fit.
+bool latent_prompt_attention_fits(int D, int R, int CR, int VD);
+bool latent_prompt_attention(const void* q, const void* kx, const void* rows, const void* v, const int* lens, int B, int S, int H, int D,
+                             int R, int CR, int VD, int window, float scale, void* out, cudaStream_t s);
 void window_softmax(const float* scores, long rows, int span, float scale, int ring_mode, int H, int Qb, int nblk, int w_eff, int window,
                     const int* pos0, const int* lens, void* out, int out_bf16, cudaStream_t s);
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,

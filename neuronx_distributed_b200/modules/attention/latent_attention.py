@@ -11,7 +11,9 @@ neither keys nor values are expanded, the weighted sum of latents comes back and
 per ring chunk scores all heads against the chunk's rows and weights the same rows, a second merges the chunks' partial softmaxes
 (``csrc/seqmix/latent_decode.cu``; rows wider than the kernel's limit go through matrix products over the gathered ring).  Prompts are
 bound by arithmetic, so they expand every head's keys and values once and spend ``dim + rot_dim + vdim`` multiply-adds per
-(query, key, head) instead of ``2 kv_rank + rot_dim``.  With ``block_products=False`` both run the one-kernel absorbed form."""
+(query, key, head) instead of ``2 kv_rank + rot_dim``: in bfloat16 with sizes in whole 16s as ONE kernel that keeps scores and
+weights on chip (``csrc/seqmix/latent_prefill.cu``), otherwise (float, odd sizes) as block matrix products around a float softmax
+kernel.  With ``block_products=False`` both run the one-kernel absorbed form."""
 from __future__ import annotations
 
 from typing import Dict, Tuple
@@ -32,6 +34,7 @@ class LatentWindowAttention(nn.Module):
         self.window, self.scale, self.rot_dims, self.eps, self.dtype = window, scale, rot_dims, eps, dtype
         self.ring = max(1, min(window, max_seq_len))
         self.block_products, self.query_block = block_products, query_block
+        self.fused_prompt = True          # bfloat16 prompts of fitting sizes in one kernel (csrc/seqmix/latent_prefill.cu)
         self.max_seq_len = max_seq_len
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
         f32 = lambda *s: nn.Parameter(torch.ones(*s, dtype=torch.float32, device=device), requires_grad=False)
@@ -54,7 +57,13 @@ class LatentWindowAttention(nn.Module):
                                       want_rows=ctx.fresh)
         seqmix.rope_q_(q, D, self.rot_dims, self.inv_freq, ctx.pos0)
         if ctx.fresh and self.block_products:
-            return F.linear(self._attend_prompt(q, rows, ctx), self.o).view(B, S, -1)
+            if self.fused_prompt and seqmix.latent_prompt_fused_ok(q, D, R, self.kv_rank + R, self.vdim):
+                c = rows[..., :self.kv_rank]
+                kx, vx = F.linear(c, self.uk.view(H * D, -1)), F.linear(c, self.uv.view(H * self.vdim, -1))
+                heads = seqmix.latent_prompt_attention(q, kx, rows, vx, ctx.lens, D, R, self.vdim, self.window, self.scale)
+            else:
+                heads = self._attend_prompt(q, rows, ctx)
+            return F.linear(heads, self.o).view(B, S, -1)
         qa = torch.bmm(q.view(N, H, D + R)[:, :, :D].transpose(0, 1), self.uk)                       # [H,N,D] @ [H,D,C]
         if S == 1 and not ctx.fresh and self.kv_rank + R <= seqmix.LATENT_ROW_MAX:
             o = seqmix.latent_window_attention(qa, q, D, st["kv"], ctx.slots, ctx.pos0, ctx.lens, self.window, self.scale)

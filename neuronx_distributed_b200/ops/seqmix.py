@@ -201,6 +201,20 @@ def latent_window_attention(qa: torch.Tensor, q: torch.Tensor, off: int, keys: t
     return o.permute(2, 0, 1, 3).reshape(H, N, C).to(qa.dtype)
 
 
+def latent_prompt_fused_ok(q: torch.Tensor, D: int, R: int, CR: int, VD: int) -> bool:
+    """True when the one-kernel prompt attention takes this call: bfloat16 on the GPU, sizes in whole 16s (8s for the parts)."""
+    return _cuda(q) and q.dtype == torch.bfloat16 and ext().latent_prompt_attention_fits(D, R, CR, VD)
+
+
+def latent_prompt_attention(q: torch.Tensor, kx: torch.Tensor, rows: torch.Tensor, v: torch.Tensor, lens: torch.Tensor, D: int, R: int,
+                            VD: int, window: int, scale: float) -> torch.Tensor:
+    """Prompts that start at position 0, expanded form, one kernel (GPU, bfloat16): ``q [B,S,H,D+R]`` rotated queries, ``kx
+    [B,S,H*D]`` every head's unrotated keys, ``rows [B,S,CR]`` whose last R numbers are the rotated key part all heads share, ``v
+    [B,S,H*VD]``.  Query i sees ``i - window < j <= i``.  Returns the heads' outputs ``[B*S, H*VD]``; padded rows give zeros."""
+    _ext.count_launch()
+    return ext().latent_prompt_attention(q, kx.contiguous(), rows, v.contiguous(), _i32(lens), D, R, VD, window, scale)
+
+
 def window_softmax(scores: torch.Tensor, scale: float, ring_mode: bool, H: int, Qb: int, nblk: int, w_eff: int, window: int,
                    pos0: torch.Tensor, lens: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """Softmax over the visible keys of float score rows made by block matrix products; masked entries come out as zeros.

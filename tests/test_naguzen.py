@@ -600,3 +600,38 @@ def test_bfloat16_routed_ffn_rows_with_a_clear_choice(rows, width, ff):
     got = m(h.cuda()).cpu().double()
     assert clear.sum() >= rows // 2
     assert torch.allclose(got[clear], want[clear], atol=3e-2, rtol=3e-2)
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,dim,rot,vdim,rank", [(3, 24, 8, 32, 48), (2, 64, 32, 64, 40), (1, 128, 64, 128, 96), (2, 8, 8, 16, 16)])
+@pytest.mark.parametrize("window", [1, 7, 64, 100, 1000])
+def test_bfloat16_prompt_attention_in_one_kernel(heads, dim, rot, vdim, rank, window):
+    """The one-kernel prompt attention (scores and weights stay on chip) against the float oracle run on the same bfloat16 weights, for
+    unequal prompts whose lengths sit around the kernel's 64-row tiles and windows below, at and above them; padded rows give zeros;
+    the ring it leaves serves the next token."""
+    from neuronx_distributed_b200.modules.attention.latent_attention import LatentWindowAttention
+
+    spec = attn_spec(heads=heads, dim=dim, rot=rot, vdim=vdim, kv_rank=rank, q_rank=40, window=window)
+    cfg = make_cfg([spec], width=64)
+    w = random_checkpoint(cfg, seed=window)
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    m = build(cfg, w, "cuda", dtype=torch.bfloat16, batch_size=4)
+    att = m.lm.layers[0].mixer
+    assert isinstance(att, LatentWindowAttention) and seqmix.latent_prompt_fused_ok(torch.zeros(1, device="cuda", dtype=torch.bfloat16), dim, rot, rank + rot, vdim)
+    lens = [130, 64, 65, 3]
+    toks = [tokens_for(cfg, n + 2, 50 + n) for n in lens]
+    ids = torch.zeros(4, max(lens), dtype=torch.long)
+    for b, t in enumerate(toks):
+        ids[b, :lens[b]] = torch.tensor(t[:lens[b]])
+    slots = [m.states.alloc() for _ in lens]
+    runs = {}
+    for fused in (True, False):
+        att.fused_prompt = fused
+        x = m.forward_step(ids.cuda(), lens, slots, [0] * 4, True)
+        runs[fused] = torch.stack([m.logits(x[b, lens[b] - 1:lens[b]])[0] for b in range(4)]).cpu()
+        nxt = m.forward_step(torch.tensor([[t[n]] for t, n in zip(toks, lens)]).cuda(), [1] * 4, slots, lens, False)
+        runs[fused, "next"] = m.logits(nxt[:, 0]).cpu()
+    want = torch.stack([oracle.forward(full, w, t[:n + 1])[0][n - 1:n + 1] for t, n in zip(toks, lens)])
+    for fused in (True, False):
+        close(runs[fused], want[:, 0], 4e-2)
+        close(runs[fused, "next"], want[:, 1], 4e-2)
+    close(runs[True], runs[False], 2e-2)

@@ -2,7 +2,8 @@
 beside the framework's closest existing model — Llama through ``LlamaForInference`` — at equal width, depth and feed-forward
 parameter count; plus every sequence-mixer kernel timed alone against the measured copy bandwidth / GEMM throughput, beside the
 like kernel of the Llama path.  One GPU, bfloat16.  Device time (CUDA events), >= 3 warm-up iterations; the weights of either
-model (> 1 GB) exceed L2, and the kernel timings flush L2 (a 512 MiB write) between iterations.
+model (> 1 GB) exceed L2, and the kernel timings flush L2 (a 512 MiB write) between iterations; every kernel row is
+replayed from a CUDA graph, so that short kernels show their device time and not the host's launch time.
 
 Layers: latent attention + dense | gla + routed | rglru + dense | latent attention + routed, width 2048: attention 16 heads of
 128 + 64 rotated, value 128, latents 512 / 1536, window 1024; gla 4 heads, key 256, value 512; rglru width 2048 in 8 blocks;
@@ -149,8 +150,26 @@ def kernel_table(dev, steps, warmup):
     lens, slots, pos0 = torch.full((B,), S, dtype=i32, device=dev), torch.arange(B, dtype=i32, device=dev), torch.zeros(B, dtype=i32, device=dev)
     rows = []
 
+    def replayed(fn):
+        """fn captured in a CUDA graph, so that the device time of short kernels is not the host's launch time."""
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            return g.replay
+        except Exception:
+            torch.cuda.synchronize()
+            return fn
+
     def add(name, fn, bytes_=0, flops=0, like=None):
-        ms = _timed(fn, steps, warmup, flush)
+        ms = _timed(replayed(fn), steps, warmup, flush)
         r = {"kernel": name, "ms": round(ms, 4)}
         if bytes_:
             r["gbs"] = round(bytes_ / ms / 1e6, 1)
