@@ -80,19 +80,30 @@ latent_prompt_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     for (int n = 0; n < 2 * VD16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
     const int i0 = q0 + r0 + g, i1 = i0 + 8;               // this thread's two queries
+    const float scale2 = scale * 1.4426950408889634f;
     const int jlo = max(0, q0 - window + 1), jhi = min(q0 + kQT - 1, len - 1);
     // key / value tiles arrive by asynchronous copies, one tile ahead of the arithmetic (two stages)
     auto fetch = [&](int kt, int st) {
         const int j0 = kt * kKT;
         bf16 *Kd = Kst(st), *Vd = Vst(st);
-        for (int i = tid; i < kKT * (DK / 8); i += 128) {
-            const int r = i / (DK / 8), c = (i % (DK / 8)) * 8, j = j0 + r, jj = min(j, len - 1);
-            const bf16* src = c < D ? kx + (((long)b * S + jj) * H + h) * D + c : rows + ((long)b * S + jj) * CR + (CR - R) + (c - D);
-            cp16(Kd + r * ldk + c, src, j < len);
+        // a warp per key row and pass, a lane per 16-byte piece (cheap index arithmetic: this runs once per tile and thread)
+        for (int c = lane * 8; c < DK; c += 256) {
+            const bool lo = c < D;
+            const long off = lo ? (long)h * D + c : (long)(CR - R) + (c - D), stride = lo ? (long)H * D : (long)CR;
+            const bf16* base = (lo ? kx : rows) + (long)b * S * stride + off;
+#pragma unroll 4
+            for (int r = warp; r < kKT; r += 4) {
+                const int j = j0 + r;
+                cp16(Kd + r * ldk + c, base + (long)min(j, len - 1) * stride, j < len);
+            }
         }
-        for (int i = tid; i < kKT * (VD / 8); i += 128) {
-            const int r = i / (VD / 8), c = (i % (VD / 8)) * 8, j = j0 + r, jj = min(j, len - 1);
-            cp16(Vd + r * ldv + c, v + (((long)b * S + jj) * H + h) * VD + c, j < len);
+        for (int c = lane * 8; c < VD; c += 256) {
+            const bf16* base = v + ((long)b * S * H + h) * VD + c;
+#pragma unroll 4
+            for (int r = warp; r < kKT; r += 4) {
+                const int j = j0 + r;
+                cp16(Vd + r * ldv + c, base + (long)min(j, len - 1) * H * VD, j < len);
+            }
         }
         cp_commit();
     };
@@ -119,15 +130,21 @@ latent_prompt_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 }
             }
         }
-        // scale, mask, running softmax (float); a thread holds 16 scores of query i0 and 16 of i1
+        // scale, mask, running softmax (float, in base 2: scores carry scale * log2(e)); a thread holds 16 scores of query i0 and 16
+        // of i1.  A tile that every query of the warp sees in full needs no mask.
+        const int wlo = q0 + r0, whi = wlo + 15;
+        const bool full = j0 + kKT - 1 <= wlo && j0 > whi - window && j0 + kKT - 1 < len;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = j0 + n * 8 + tq * 2 + (e & 1), i = (e < 2) ? i0 : i1;
-                const bool vis = j <= i && j > i - window && j < len;
-                sacc[n][e] = vis ? sacc[n][e] * scale : -INFINITY;
+                bool vis = true;
+                if (!full) {
+                    const int j = j0 + n * 8 + tq * 2 + (e & 1), i = (e < 2) ? i0 : i1;
+                    vis = j <= i && j > i - window && j < len;
+                }
+                sacc[n][e] = vis ? sacc[n][e] * scale2 : -INFINITY;
                 mx[e >> 1] = fmaxf(mx[e >> 1], sacc[n][e]);
             }
         float corr[2], base[2];
@@ -137,7 +154,7 @@ latent_prompt_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float mn = fmaxf(mrow[r], mx[r]);
             base[r] = mn == -INFINITY ? 0.f : mn;          // nothing visible so far: every weight is exp(-inf) = 0
-            corr[r] = expf(mrow[r] - base[r]);
+            corr[r] = exp2f(mrow[r] - base[r]);
             mrow[r] = mn;
         }
         float ls[2] = {0.f, 0.f};
@@ -145,7 +162,7 @@ latent_prompt_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                sacc[n][e] = expf(sacc[n][e] - base[e >> 1]);
+                sacc[n][e] = exp2f(sacc[n][e] - base[e >> 1]);
                 ls[e >> 1] += sacc[n][e];
             }
 #pragma unroll

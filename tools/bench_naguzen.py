@@ -26,9 +26,9 @@ def naguzen_layers():
                        "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "mask": {"size": 1024},
                                  "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192)}}
     dense = {"kind": "dense", "ff": 8192}
-    moe = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4, "scale": 2.5}, "shared": {"ff": 2048}}
+    moe = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4, "scale": 2.0}, "shared": {"ff": 2048}}
     return [att(dense),
-            {"type": "gla", "mlp": moe, "mixer": {"heads": 4, "dim": 256, "vdim": 512, "tau": 16.0, "decay_rank": 16}},
+            {"type": "gla", "mlp": moe, "mixer": {"heads": 4, "dim": 256, "vdim": 512, "tau": 8.0, "decay_rank": 16}},
             {"type": "rglru", "mlp": dense, "mixer": {"width": 2048, "blocks": 8, "conv": 4}},
             att(moe)]
 
@@ -214,8 +214,11 @@ def kernel_table(dev, steps, warmup):
     keys = rnd(B, S, C + R)
     pairs = B * H * sum(min(p + 1, win) for p in range(S))
     ctx = StepContext(lens, slots, pos0, True)
-    add("latent attention prompt (expand keys / values, block products, window softmax; window 1024)",
+    add("latent attention prompt as block products (expand keys / values, cuBLAS, float window softmax; window 1024)",
         lambda: att._attend_prompt(q, keys, ctx), flops=pairs * 2 * (D + R + Vd) + 2 * N * C * H * (D + Vd))
+    kx, vx = rnd(B, S, H * D), rnd(B, S, H * Vd)
+    add("latent attention prompt, one kernel (mma.sync scores, float window softmax, value product on chip; window 1024)",
+        lambda: seqmix.latent_prompt_attention(q, kx, keys, vx, lens, D, R, Vd, win, 0.07), flops=pairs * 2 * (D + R + Vd))
     qf, kf, vf = rnd(B, S, H, 128), rnd(B, S, 4, 128), rnd(B, S, 4, 128)
     add("llama flash_attention prompt (causal, full)", lambda: ops.attention.flash_attention(qf, kf, vf, causal=True),
         flops=4 * B * H * 128 * S * (S + 1) / 2, like="latent attention prompt")
