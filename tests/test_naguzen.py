@@ -167,10 +167,12 @@ def test_short_conv_prompt_then_tokens(device, taps, residual, bias):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-def test_norms_and_activations(device):
+@pytest.mark.parametrize("rows,C", [(11, 70), (3, 520), (5, 515), (1300, 72), (1200, 516)])
+def test_norms_and_activations(device, rows, C):
+    """Few and many rows, narrow and wide, in whole fours and not: every launch shape of the norm kernels."""
     g = torch.Generator().manual_seed(1)
-    x, gate, res = torch.randn(11, 70, generator=g) * 3, torch.randn(11, 70, generator=g), torch.randn(11, 70, generator=g)
-    w, one = torch.rand(70, generator=g) + 0.5, torch.tensor([0.37])
+    x, gate, res = torch.randn(rows, C, generator=g) * 3, torch.randn(rows, C, generator=g), torch.randn(rows, C, generator=g)
+    w, one = torch.rand(C, generator=g) + 0.5, torch.tensor([0.37])
     eps = 1e-3
     dv = lambda t: t.to(device)
     want = oracle.rms(x.double(), eps)
@@ -178,8 +180,8 @@ def test_norms_and_activations(device):
     assert torch.allclose(seqmix.rms_norm(dv(x), dv(one), eps).cpu().double(), want * 0.37, atol=1e-5)
     gated = seqmix.rms_norm(dv(x), dv(w), eps, gate=dv(gate)).cpu().double()
     assert torch.allclose(gated, want * w * (gate * torch.sigmoid(gate)).double(), atol=1e-5)
-    wide = torch.randn(11, 90, generator=g)                                     # a norm over the first columns of wider rows
-    assert torch.allclose(seqmix.rms_norm(dv(wide)[:, :70], dv(w), eps).cpu().double(), oracle.rms(wide[:, :70].double(), eps) * w, atol=1e-5)
+    wide = torch.randn(rows, C + 20, generator=g)                               # a norm over the first columns of wider rows
+    assert torch.allclose(seqmix.rms_norm(dv(wide)[:, :C], dv(w), eps).cpu().double(), oracle.rms(wide[:, :C].double(), eps) * w, atol=1e-5)
     r = dv(res.clone())
     seqmix.add_rms_norm_(r, dv(x), dv(one), eps)
     assert torch.allclose(r.cpu().double(), res.double() + want * 0.37, atol=1e-5)
@@ -207,6 +209,34 @@ def test_routed_ffn(device, rows, top, shared):
     h = torch.randn(rows, cfg["width"], generator=torch.Generator().manual_seed(3))
     want = oracle.moe_ff(h.double(), {k: v.double() for k, v in P.items()}, f)
     assert torch.allclose(m(h.to(device)).cpu().double(), want, atol=2e-5)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("I,O", [(264, 19), (48, 7), (131, 5), (1024, 3)])
+def test_expert_streaming_gemv(device, I, O):
+    """Rows that each name their own matrix of a stack: inner sizes below, at and above one pass of a warp, in whole fours and not."""
+    g = torch.Generator().manual_seed(I)
+    w, x = torch.randn(5, O, I, generator=g), torch.randn(6, I, generator=g)
+    sel = torch.tensor([4, 0, 0, 3, 1, 4])
+    want = torch.einsum("moi,mi->mo", w[sel].double(), x.double())
+    got = seqmix.indexed_gemv(w.to(device), sel.to(device), x.to(device), False).cpu().double()
+    assert torch.allclose(got, want, atol=1e-4)
+    got = seqmix.indexed_gemv(w.to(device), sel.to(device), x.to(device), True).cpu().double()
+    assert torch.allclose(got, oracle.gelu_erf(want), atol=1e-4)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("heads,window", [(11, 6), (8, 40), (17, 33)])
+def test_many_heads_and_rings_of_several_chunks(device, heads, window):
+    """More heads than one block of the single-token attention kernel takes, and rings longer than one of its chunks: a prompt, then
+    tokens one by one until the window has passed over decoded tokens, against the oracle at every position."""
+    cfg = make_cfg([attn_spec(heads=heads, dim=16, rot=8, vdim=24, kv_rank=40, q_rank=24, window=window, mlp=None)])
+    w = random_checkpoint(cfg, seed=heads)
+    full = complete_config(cfg, {k: v.shape for k, v in w.items()})
+    toks = tokens_for(cfg, window + 45, 7)
+    want = oracle.forward(full, w, toks)[0]
+    close(run_alone(build(cfg, w, device), toks, 5), want, TOL32)
+    close(run_alone(build(cfg, w, device), toks, window + 3), want, TOL32)
 
 
 def test_routed_ffn_blockwise_layout(monkeypatch):
