@@ -34,10 +34,25 @@ class RoutedFFN(nn.Module):
         self.up, self.down = mk(experts, ff, width), mk(experts, width, ff)
         if shared_ff:
             self.shared_up, self.shared_down = mk(shared_ff, width), mk(width, shared_ff)
+        self._router_lowp = None       # (version of the router matrix, its bfloat16 transpose or None when that would round)
+
+    def _router_logits(self, h: torch.Tensor) -> torch.Tensor:
+        """Float logits.  When the activations are bfloat16 and the (float) router matrix holds only numbers that bfloat16 represents
+        exactly — a checkpoint stored in bfloat16 — the product runs on the bfloat16 operands with float accumulation: the same
+        products and a float sum, on the tensor cores.  Otherwise the framework router's float product."""
+        w = self.router.linear_router.weight
+        if h.dtype != torch.bfloat16 or not h.is_cuda or self.router.linear_router.bias is not None:
+            return self.router.get_router_logits(h)
+        if self._router_lowp is None or self._router_lowp[0] != w._version:
+            low = w.detach().to(torch.bfloat16)
+            self._router_lowp = (w._version, low.t().contiguous() if bool((low.float() == w).all()) else None)
+        if self._router_lowp[1] is None:
+            return self.router.get_router_logits(h)
+        return seqmix.matmul_f32(h[None], self._router_lowp[1][None])[0]
 
     def route(self, h: torch.Tensor):
         """Float scores of all experts → (weights ``[N, top]`` float, expert ids ``[N, top]``)."""
-        scores = self.router.apply_activation_fn(self.router.get_router_logits(h))
+        scores = self.router.apply_activation_fn(self._router_logits(h))
         w, idx = torch.topk(scores, self.top, dim=-1)
         return w * self.weight_scale, idx
 
