@@ -74,6 +74,8 @@ def build_naguzen(dev, batch, max_len):
         for name, p in m.named_parameters():
             if p.dtype == torch.bfloat16 or "router" in name or "gate_" in name and "bias" not in name:
                 p.normal_(0.0, 0.02 if p.dim() > 1 else 0.0, generator=g)
+                if "router" in name:                       # as a checkpoint stored in bfloat16 would hold it
+                    p.copy_(p.to(torch.bfloat16).float())
             elif name.endswith(("norm.weight", "norm1.weight", "norm2.weight", "dq_norm", "dkv_norm", "mixer.norm")):
                 p.fill_(1.0)
             elif "a2_bias" in name:
