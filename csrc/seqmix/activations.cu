@@ -103,9 +103,31 @@ void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_s
 #undef SEQMIX_IGEMV
 }
 
+// four columns per thread (C and the bases in whole fours)
+template <typename T>
+__global__ void moe_combine_vec_kernel(const T* __restrict__ rows, const int* __restrict__ src, const float* __restrict__ weight,
+                                       const T* __restrict__ base, int N, int top, int C, T* __restrict__ out) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4, n = blockIdx.y;
+    if (c >= C) return;
+    float4 acc = base ? ld4(base + (long)n * C + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top; ++k) {
+        const float w = weight[(long)n * top + k];
+        const float4 r = ld4(rows + (long)src[(long)n * top + k] * C + c);
+        acc.x = fmaf(w, r.x, acc.x); acc.y = fmaf(w, r.y, acc.y); acc.z = fmaf(w, r.z, acc.z); acc.w = fmaf(w, r.w, acc.w);
+    }
+    st4(out + (long)n * C + c, acc);
+}
+
 void moe_combine(const void* rows, const int* src, const float* weight, const void* base, int bf, int N, int top, int C, void* out,
                  cudaStream_t s) {
     if (N == 0) return;
+    const size_t a4 = bf ? 8 : 16;
+    if (C % 4 == 0 && (uintptr_t)rows % a4 == 0 && (uintptr_t)out % a4 == 0 && (base == nullptr || (uintptr_t)base % a4 == 0)) {
+        dim3 vblock(128), vgrid((C / 4 + 127) / 128, N);
+        if (bf) moe_combine_vec_kernel<bf16><<<vgrid, vblock, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, N, top, C, (bf16*)out);
+        else moe_combine_vec_kernel<float><<<vgrid, vblock, 0, s>>>((const float*)rows, src, weight, (const float*)base, N, top, C, (float*)out);
+        return;
+    }
     dim3 block(128), grid((C + 127) / 128, N);
     if (bf) moe_combine_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, N, top, C, (bf16*)out);
     else moe_combine_kernel<float><<<grid, block, 0, s>>>((const float*)rows, src, weight, (const float*)base, N, top, C, (float*)out);

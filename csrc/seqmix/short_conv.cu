@@ -67,7 +67,8 @@ __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_s
 // the block of the first 64 tokens can touch the carried history, and it replaces it after its own reads.
 constexpr int kVecTaps = 8, kRun = 8;
 
-template <typename Tin, typename Tout>
+// VT: taps the registers are laid out for (4 or 8; the real count is an argument)
+template <typename Tin, typename Tout, int VT>
 __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long x_st, const float* __restrict__ w,
                                       const float* __restrict__ bias, Tin* state, const int* __restrict__ slots,
                                       const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual,
@@ -83,17 +84,17 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
         return zero;
     };
     if (c < C) {
-        float4 wr[kVecTaps], prev[kVecTaps - 1];          // right-aligned: wr[kVecTaps-1] weighs the current token
+        float4 wr[VT], prev[VT - 1];          // right-aligned: wr[VT-1] weighs the current token
 #pragma unroll
-        for (int k = 0; k < kVecTaps; ++k) {
-            const int j = k - (kVecTaps - taps);
+        for (int k = 0; k < VT; ++k) {
+            const int j = k - (VT - taps);
             wr[k] = j >= 0 ? make_float4(w[(long)c * taps + j], w[(long)(c + 1) * taps + j], w[(long)(c + 2) * taps + j], w[(long)(c + 3) * taps + j]) : zero;
         }
         const float4 bc = bias ? ld4(bias + c) : zero;
 #pragma unroll
-        for (int k = 0; k < kVecTaps - 1; ++k) {
-            const int s = tbase - (kVecTaps - 1) + k;
-            prev[k] = (k >= kVecTaps - 1 - hist && tbase < len) ? in4(s) : zero;
+        for (int k = 0; k < VT - 1; ++k) {
+            const int s = tbase - (VT - 1) + k;
+            prev[k] = (k >= VT - 1 - hist && tbase < len) ? in4(s) : zero;
         }
         float4 run[kRun];                                 // the run's own inputs, all loads in flight together
 #pragma unroll
@@ -107,30 +108,30 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
                 if (t < len) {
                     acc = bc;
 #pragma unroll
-                    for (int k = 0; k < kVecTaps - 1; ++k) {
+                    for (int k = 0; k < VT - 1; ++k) {
                         acc.x = fmaf(wr[k].x, prev[k].x, acc.x); acc.y = fmaf(wr[k].y, prev[k].y, acc.y);
                         acc.z = fmaf(wr[k].z, prev[k].z, acc.z); acc.w = fmaf(wr[k].w, prev[k].w, acc.w);
                     }
-                    const float4 wl = wr[kVecTaps - 1];
+                    const float4 wl = wr[VT - 1];
                     acc.x = fmaf(wl.x, cur.x, acc.x); acc.y = fmaf(wl.y, cur.y, acc.y);
                     acc.z = fmaf(wl.z, cur.z, acc.z); acc.w = fmaf(wl.w, cur.w, acc.w);
                     if (residual) { acc.x += cur.x; acc.y += cur.y; acc.z += cur.z; acc.w += cur.w; }
                 }
                 st4(out + ((long)b * S + t) * C + c, acc);
 #pragma unroll
-                for (int k = 0; k < kVecTaps - 2; ++k) prev[k] = prev[k + 1];
-                prev[kVecTaps - 2] = cur;
+                for (int k = 0; k < VT - 2; ++k) prev[k] = prev[k + 1];
+                prev[VT - 2] = cur;
             }
         }
     }
     if (blockIdx.y != 0) return;
     __syncthreads();   // every read of the old history is done before it is replaced
     if (threadIdx.y == 0 && c < C && hist > 0) {
-        float4 nh[kVecTaps - 1];
+        float4 nh[VT - 1];
 #pragma unroll
-        for (int i = 0; i < kVecTaps - 1; ++i) nh[i] = i < hist ? in4(len - hist + i) : zero;
+        for (int i = 0; i < VT - 1; ++i) nh[i] = i < hist ? in4(len - hist + i) : zero;
 #pragma unroll
-        for (int i = 0; i < kVecTaps - 1; ++i)
+        for (int i = 0; i < VT - 1; ++i)
             if (i < hist) st4(st + (long)i * C + c, nh[i]);
     }
 }
@@ -142,8 +143,12 @@ static void launch(const void* x, long x_sb, long x_st, const float* w, const fl
                      (uintptr_t)state % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0);
     if (vec) {
         dim3 grid((C / 4 + 31) / 32, (S + kRun * 8 - 1) / (kRun * 8), B), block(32, 8);
-        short_conv_vec_kernel<Tin, Tout><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
-                                                               fresh, residual, (Tout*)out);
+        if (taps <= 4)
+            short_conv_vec_kernel<Tin, Tout, 4><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
+                                                                      fresh, residual, (Tout*)out);
+        else
+            short_conv_vec_kernel<Tin, Tout, 8><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
+                                                                      fresh, residual, (Tout*)out);
         return;
     }
     int ty = S >= 16 ? 16 : (S >= 4 ? 4 : 1);
