@@ -17,17 +17,17 @@ static const int kRowRegs = 20;  // row coordinates per lane: C + R <= 32 * kRow
 static const int kColsPerThread = 2;   // value columns per thread: C <= kColsPerThread * kThreads
 
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, const T* __restrict__ qr, long qr_sn, long qr_sh,
                            const T* __restrict__ keys, long key_sb, int ring, const int* __restrict__ key_index,
                            const int* __restrict__ pos0, const int* __restrict__ lens, int H, int C, int R, int window, float scale,
                            int nsplit, float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc) {
     extern __shared__ float smem[];
-    const int CR = C + R, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int CR = C + R, CRp = (CR + 31) & ~31, nE = CRp / 32, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int split = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * kHeads, nh = min(kHeads, H - h0);
-    float* sq = smem;                          // [kHeads][CR]
-    float* sk = sq + kHeads * CR;              // [kChunk][CR]
-    float* sp = sk + kChunk * CR;              // [kHeads][kChunk] scores
+    float* sq = smem;                          // [kHeads][CRp]  (rows padded with zeros to whole 32s: no bounds in the inner loops)
+    float* sk = sq + kHeads * CRp;             // [kChunk][CRp]
+    float* sp = sk + kChunk * CRp;             // [kHeads][kChunk] scores
     float* sw = sp + kHeads * kChunk;          // [kChunk][kHeads] weights
     const int p = pos0[b], r0 = split * kChunk, nr = min(kChunk, ring - r0);
     const long pbase = ((long)b * nsplit + split) * H + h0;
@@ -37,15 +37,19 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
         if (m < 0) m += ring;
         return p - m >= 0 && m < window;
     };
-    bool any = false;
-    if (lens[b] > 0)
-        for (int j = 0; j < nr; ++j) any = any || visible(r0 + j);
+    // one lane per ring row of the chunk: the mask of visible rows, the same in every warp
+    const unsigned vismask = __ballot_sync(0xffffffffu, lens[b] > 0 && lane < nr && visible(r0 + lane));
+    const bool any = vismask != 0u;
     if (!any) {                                // nothing to see here: an empty partial with weight zero
         if (tid < nh) { part_m[pbase + tid] = -INFINITY; part_l[pbase + tid] = 0.f; }
         for (int i = tid; i < nh * C; i += kThreads) part_acc[pbase * C + i] = 0.f;
         return;
     }
     const T* base = keys + (long)(key_index ? key_index[b] : b) * key_sb + (long)r0 * CR;
+    if (nh < kHeads || CR != CRp) {            // heads past the tile's last and the rows' padding read as zeros
+        for (int i = tid; i < (kHeads + kChunk) * CRp; i += kThreads) sq[i] = 0.f;
+        __syncthreads();
+    }
     if (VEC) {                                 // every extent and stride a multiple of four elements, aligned bases
         const int CR4 = CR / 4;
         constexpr int kBatch = 8;              // loads in flight per thread
@@ -55,7 +59,10 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) { const int i = i0 + u * kThreads + tid; v[u] = i < nr * CR4 ? ld4(base + 4 * i) : zero; }
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) { const int i = i0 + u * kThreads + tid; if (i < nr * CR4) *reinterpret_cast<float4*>(sk + 4 * i) = v[u]; }
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = i0 + u * kThreads + tid;
+                if (i < nr * CR4) *reinterpret_cast<float4*>(sk + (i / CR4) * CRp + (i % CR4) * 4) = v[u];
+            }
         }
         for (int i0 = 0; i0 < nh * CR4; i0 += kBatch * kThreads) {
             float4 v[kBatch];
@@ -68,14 +75,14 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
                 const int i = i0 + u * kThreads + tid;
-                if (i < nh * CR4) *reinterpret_cast<float4*>(sq + 4 * i) = v[u];
+                if (i < nh * CR4) *reinterpret_cast<float4*>(sq + (i / CR4) * CRp + (i % CR4) * 4) = v[u];
             }
         }
     } else {
-        for (int i = tid; i < nr * CR; i += kThreads) sk[i] = ldf(base + i);
+        for (int i = tid; i < nr * CR; i += kThreads) sk[(i / CR) * CRp + i % CR] = ldf(base + i);
         for (int i = tid; i < nh * CR; i += kThreads) {
             const int h = i / CR, d = i % CR;
-            sq[i] = d < C ? ldf(qa + (long)b * qa_sn + (long)(h0 + h) * qa_sh + d) : ldf(qr + (long)b * qr_sn + (long)(h0 + h) * qr_sh + d - C);
+            sq[h * CRp + d] = d < C ? ldf(qa + (long)b * qa_sn + (long)(h0 + h) * qa_sh + d) : ldf(qr + (long)b * qr_sn + (long)(h0 + h) * qr_sh + d - C);
         }
     }
     __syncthreads();
@@ -86,19 +93,19 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
         float ka[kRowRegs], kb[kRowRegs];
 #pragma unroll
         for (int e = 0; e < kRowRegs; ++e) {
-            const int d = e * 32 + lane;
-            ka[e] = d < CR ? sk[j0 * CR + d] : 0.f;
-            kb[e] = d < CR && two ? sk[j1 * CR + d] : 0.f;
+            if (e < nE) {
+                ka[e] = sk[j0 * CRp + e * 32 + lane];
+                kb[e] = two ? sk[j1 * CRp + e * 32 + lane] : 0.f;
+            }
         }
         for (int h = 0; h < nh; h += 4) {
             float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < kRowRegs; ++e) {
-                const int d = e * 32 + lane;
-                if (e * 32 < CR && d < CR) {
+                if (e < nE) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const float qv = h + g < nh ? sq[(h + g) * CR + d] : 0.f;
+                        const float qv = sq[(h + g) * CRp + e * 32 + lane];
                         pa[g] = fmaf(qv, ka[e], pa[g]);
                         pb[g] = fmaf(qv, kb[e], pb[g]);
                     }
@@ -122,7 +129,7 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
     for (int i = tid; i < kChunk * kHeads; i += kThreads) sw[i] = 0.f;
     __syncthreads();
     for (int h = warp; h < nh; h += kThreads / 32) {
-        const bool vis = lane < nr && visible(r0 + lane);
+        const bool vis = (vismask >> lane) & 1u;
         const float s = vis ? sp[h * kChunk + lane] : -INFINITY;
         float mx = s;
 #pragma unroll
@@ -144,7 +151,7 @@ latent_ring_partial_kernel(const T* __restrict__ qa, long qa_sn, long qa_sh, con
 #pragma unroll
         for (int e = 0; e < kColsPerThread; ++e) {
             const int c = tid + e * kThreads;
-            kv[e] = c < C ? sk[j * CR + c] : 0.f;
+            kv[e] = c < C ? sk[j * CRp + c] : 0.f;
         }
         float w[kHeads];                          // the same addresses for the whole warp
 #pragma unroll
@@ -211,7 +218,7 @@ __global__ void latent_ring_merge_kernel(const float* __restrict__ part_m, const
 int latent_ring_decode_splits(int ring) { return (ring + kChunk - 1) / kChunk; }
 
 bool latent_ring_decode_fits(int C, int R) {
-    return C <= kColsPerThread * kThreads && C + R <= 32 * kRowRegs && (size_t)((kHeads + kChunk) * (C + R) + 2 * kHeads * kChunk) * sizeof(float) <= 200 * 1024;
+    return C <= kColsPerThread * kThreads && C + R <= 32 * kRowRegs && (size_t)((kHeads + kChunk) * ((C + R + 31) & ~31) + 2 * kHeads * kChunk) * sizeof(float) <= 200 * 1024;
 }
 
 template <typename T>
@@ -220,7 +227,7 @@ static void ring_decode_launch(const void* qa, long qa_sn, long qa_sh, const voi
                                float scale, float* part_m, float* part_l, float* part_acc, void* out, long out_sn, long out_sh,
                                cudaStream_t s) {
     const int nsplit = latent_ring_decode_splits(ring);
-    const size_t smem = (size_t)((kHeads + kChunk) * (C + R) + 2 * kHeads * kChunk) * sizeof(float);
+    const size_t smem = (size_t)((kHeads + kChunk) * ((C + R + 31) & ~31) + 2 * kHeads * kChunk) * sizeof(float);
     dim3 grid(nsplit, B, (H + kHeads - 1) / kHeads);
     const size_t a4 = 4 * sizeof(T);
     const bool vec = C % 4 == 0 && R % 4 == 0 && qa_sn % 4 == 0 && qa_sh % 4 == 0 && qr_sn % 4 == 0 && qr_sh % 4 == 0 && key_sb % 4 == 0 &&
