@@ -6,11 +6,21 @@ new sequence runs with ``fresh=True``, which makes every kernel ignore what the 
 The plain K/V manager next to this file (``kv_cache.py``) serves the Llama-family models: fixed batch rows, full-length caches."""
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, List, Sequence, Tuple
 
 import torch
 
 Spec = Dict[str, Tuple[Tuple[int, ...], torch.dtype]]
+
+
+@dataclasses.dataclass
+class StepContext:
+    """What every stateful layer needs to know about the rows of a step (all device tensors int32 ``[B]``)."""
+    lens: torch.Tensor          # real tokens per row in this step
+    slots: torch.Tensor         # state slot of each row
+    pos0: torch.Tensor          # position of each row's first token
+    fresh: bool                 # the rows start their sequences in this step
 
 
 class SequenceStateManager:

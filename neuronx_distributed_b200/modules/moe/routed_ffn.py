@@ -1,7 +1,12 @@
-"""Routed feed-forward with independent (non-normalised) expert weights and plain two-matrix experts, for serving:
-scores ``s = act(W_router h)`` in float (the framework's ``RouterTopK``; sigmoid here), the ``top`` largest are chosen, the output
-is ``sum_e s_e * scale * expert_e(h)`` plus an always-on shared expert.  Experts are ``W_down act(W_up h)`` without biases or
-gating, kept as stacks ``[E, ff, width]`` / ``[E, width, ff]``.
+"""Routed feed-forward with independent (non-renormalised) expert weights, for serving: scores ``s = act(W_router h)`` in float
+(the framework's ``RouterTopK``; sigmoid or softmax), the ``top`` largest are chosen, the output is
+``sum_e s_e * scale * expert_e(h)`` plus an always-on shared expert.  Experts have no biases and are kept as stacks: plain,
+``W_down gelu(W_up h)`` with ``up [E, ff, width]``, or gated, ``W_down (silu(W_gate h) * (W_up h))`` with the gate rows stacked
+over the up rows in ``up [E, 2 ff, width]``; ``down [E, width, ff]``.
+
+Two options of the router.  ``choice_bias``: a float vector added to the scores for the CHOICE only (the weights stay the plain
+scores).  ``identity_experts``: the router's last outputs name experts without tensors whose output is the input itself; their
+weights are summed per token and enter the combine as a weighted copy of the input.
 
 Two execution shapes, both summing the chosen experts in float (``moe_combine``):
 * few rows (token generation): the chosen experts' matrices are streamed once by ``indexed_gemv`` — no host synchronisation;
@@ -25,13 +30,17 @@ class RoutedFFN(nn.Module):
     small_batch_rows = 64          # up to this many (row, expert) pairs the streaming path is used
 
     def __init__(self, width: int, ff: int, experts: int, top: int, weight_scale: float = 1.0, shared_ff: int = 0,
-                 router_act: str = "sigmoid", dtype: torch.dtype = torch.bfloat16, device=None):
+                 router_act: str = "sigmoid", gated: bool = False, identity_experts: int = 0, choice_bias: bool = False,
+                 dtype: torch.dtype = torch.bfloat16, device=None):
         super().__init__()
         self.width, self.ff, self.experts, self.top, self.weight_scale, self.shared_ff = width, ff, experts, top, weight_scale, shared_ff
-        self.router = RouterTopK(experts, top, width, dtype=torch.float32, device=device, act_fn=router_act)
+        self.gated, self.identity_experts = gated, identity_experts
+        self.router = RouterTopK(experts + identity_experts, top, width, dtype=torch.float32, device=device, act_fn=router_act)
         self.router.requires_grad_(False)
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
-        self.up, self.down = mk(experts, ff, width), mk(experts, width, ff)
+        self.up, self.down = mk(experts, (2 if gated else 1) * ff, width), mk(experts, width, ff)
+        self.correction = nn.Parameter(torch.zeros(experts + identity_experts, dtype=torch.float32, device=device),
+                                       requires_grad=False) if choice_bias else None
         if shared_ff:
             self.shared_up, self.shared_down = mk(shared_ff, width), mk(width, shared_ff)
         self._router_lowp = None       # (version of the router matrix, its bfloat16 transpose or None when that would round)
@@ -53,8 +62,16 @@ class RoutedFFN(nn.Module):
     def route(self, h: torch.Tensor):
         """Float scores of all experts → (weights ``[N, top]`` float, expert ids ``[N, top]``)."""
         scores = self.router.apply_activation_fn(self._router_logits(h))
-        w, idx = torch.topk(scores, self.top, dim=-1)
-        return w * self.weight_scale, idx
+        if self.correction is None:
+            w, idx = torch.topk(scores, self.top, dim=-1)
+        else:
+            idx = torch.topk(scores + self.correction, self.top, dim=-1).indices
+            w = scores.gather(1, idx)
+        return (w * self.weight_scale if self.weight_scale != 1.0 else w), idx
+
+    def _act(self, y: torch.Tensor) -> torch.Tensor:
+        """The experts' activation on the up-projection's output: ``[M, ff]`` (plain) or ``[M, 2 ff]`` → ``[M, ff]`` (gated)."""
+        return seqmix.silu_mul(y) if self.gated else seqmix.gelu_erf(y)
 
     block_rows = 128               # rows per block of the grouped GEMM
 
@@ -79,7 +96,7 @@ class RoutedFFN(nn.Module):
         tp = tp2id[: b2e.numel() * bs].long()
         x = h[tp.clamp(min=0)]
         _ext.count_launch(2)
-        eo = e.grouped_gemm(seqmix.gelu_erf(e.grouped_gemm(x, self.up, b2e, bs, True)), self.down, b2e, bs, True)
+        eo = e.grouped_gemm(self._act(e.grouped_gemm(x, self.up, b2e, bs, True)), self.down, b2e, bs, True)
         N, top = idx.shape                                                         # no host synchronisation: padding slots write
         tok, exp = tp.clamp(min=0), b2e.long().repeat_interleave(bs)               # to a spare entry past the end
         choice = (idx[tok] == exp[:, None]).to(torch.int32).argmax(1)
@@ -93,26 +110,36 @@ class RoutedFFN(nn.Module):
         N = h.shape[0]
         w, idx = self.route(h)
         M = N * self.top
+        ident_w = None
+        if self.identity_experts:                                  # identity choices: weight moved to the input's own term
+            ident = idx >= self.experts
+            ident_w = torch.where(ident, w, torch.zeros_like(w)).sum(1)
+            w = torch.where(ident, torch.zeros_like(w), w)
         if M <= self.small_batch_rows:
-            sel = idx.reshape(-1).to(torch.int32)
-            mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), True)
-            eo = seqmix.indexed_gemv(self.down, sel, mid, False)
+            sel = idx.reshape(-1).to(torch.int32)                  # the streaming kernels skip rows that name no matrix
+            mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), "silu_glu" if self.gated else "gelu")
+            eo = seqmix.indexed_gemv(self.down, sel, mid, None)
             src = torch.arange(M, device=h.device, dtype=torch.int32).view(N, self.top)
-        elif self._grouped_kernels(h) is not None:
+        elif self._grouped_kernels(h) is not None and not self.identity_experts:
             eo, src = self._experts_grouped(h, idx)
         else:
             flat = idx.reshape(-1)
             order = torch.argsort(flat, stable=True)
-            counts = torch.bincount(flat, minlength=self.experts).tolist()
+            counts = torch.bincount(flat, minlength=self.experts + self.identity_experts).tolist()[:self.experts]
             xs = h[order // self.top]
-            eo = torch.empty(M, self.width, dtype=h.dtype, device=h.device)
+            eo = torch.zeros(M, self.width, dtype=h.dtype, device=h.device) if self.identity_experts else \
+                torch.empty(M, self.width, dtype=h.dtype, device=h.device)
             off = 0
             for e, c in enumerate(counts):
                 if c:
-                    eo[off:off + c] = F.linear(seqmix.gelu_erf(F.linear(xs[off:off + c], self.up[e])), self.down[e])
+                    eo[off:off + c] = F.linear(self._act(F.linear(xs[off:off + c], self.up[e])), self.down[e])
                     off += c
             src = torch.empty(M, dtype=torch.int32, device=h.device)
             src[order] = torch.arange(M, device=h.device, dtype=torch.int32)
             src = src.view(N, self.top)
+        if self.identity_experts:
+            if self.shared_ff:
+                raise NotImplementedError("identity experts together with a shared expert")
+            return seqmix.moe_combine(eo, src, w.contiguous(), h, ident_w)
         base = F.linear(seqmix.gelu_erf(F.linear(h, self.shared_up)), self.shared_down) if self.shared_ff else None
         return seqmix.moe_combine(eo, src, w.contiguous(), base)

@@ -81,3 +81,31 @@ class ScalarRMSNorm(nn.Module):
 
         seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight.reshape(1), self.eps)
         return res
+
+
+class OffsetRMSNorm(nn.Module):
+    """RMS norm whose checkpoint stores the gain's offset from one: ``x / sqrt(mean(x^2) + eps) * (1 + w)``.  The parameter here
+    is the gain itself, ``1 + w`` formed once in float (``set_offset``).  ``forward`` gives the sublayer's input in ``out_dtype``;
+    ``add_to(res, y)`` is the closing norm of a sandwich block, ``res += norm(y)`` with ``res`` a float stream (one kernel each,
+    ``csrc/seqmix/norms.cu``)."""
+
+    def __init__(self, width: int, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32, device=device), requires_grad=False)
+        self.eps = eps
+
+    @torch.no_grad()
+    def set_offset(self, w: torch.Tensor) -> None:
+        self.weight.copy_(1.0 + w.to(device=self.weight.device, dtype=torch.float32))
+
+    def forward(self, input: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        from ..ops import seqmix
+
+        x = input
+        return seqmix.rms_norm(x.reshape(-1, x.shape[-1]), self.weight, self.eps, None, out_dtype or x.dtype).view(x.shape)
+
+    def add_to(self, res: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        from ..ops import seqmix
+
+        seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight, self.eps)
+        return res

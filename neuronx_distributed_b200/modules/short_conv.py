@@ -22,6 +22,7 @@ class ShortConv(nn.Module):
         """Per-sequence state: the last ``taps - 1`` inputs, in the dtype the convolution reads."""
         return (self.taps - 1, self.channels), in_dtype
 
-    def forward(self, x: torch.Tensor, state: torch.Tensor, ctx, out_dtype: torch.dtype) -> torch.Tensor:
-        """``x [B,S,C]`` (last dim contiguous) → ``[B,S,C]``; ``state`` is updated in place for the rows' slots."""
-        return seqmix.short_conv(x, self.weight, self.bias, state, ctx.slots, ctx.lens, ctx.fresh, self.residual, out_dtype)
+    def forward(self, x: torch.Tensor, state: torch.Tensor, ctx, out_dtype: torch.dtype, silu: bool = False) -> torch.Tensor:
+        """``x [B,S,C]`` (last dim contiguous) → ``[B,S,C]`` (``silu`` applied when asked); ``state`` is updated in place for the
+        rows' slots."""
+        return seqmix.short_conv(x, self.weight, self.bias, state, ctx.slots, ctx.lens, ctx.fresh, self.residual, out_dtype, silu)

@@ -71,12 +71,13 @@ def _i32(t: torch.Tensor) -> torch.Tensor:
 
 # --------------------------------------------------------------------------------------------------------------- short convolution
 def short_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, slots: torch.Tensor,
-               lens: torch.Tensor, fresh: bool, residual: bool, out_dtype: torch.dtype) -> torch.Tensor:
+               lens: torch.Tensor, fresh: bool, residual: bool, out_dtype: torch.dtype, silu: bool = False) -> torch.Tensor:
     """``x [B,S,C]``, ``w [C,taps]`` float, ``state [slots, taps-1, C]`` of x's dtype (updated in place) → ``[B,S,C]``:
-    ``out_t = (x_t if residual) + bias + sum_j w[:, j] * in_(t-taps+1+j)``; rows past ``lens`` give zeros."""
+    ``out_t = act((x_t if residual) + bias + sum_j w[:, j] * in_(t-taps+1+j))`` with ``act`` the identity or ``silu``; rows past
+    ``lens`` give zeros."""
     if _cuda(x):
         _ext.count_launch()
-        return ext().short_conv(x, w, bias, state, _i32(slots), _i32(lens), fresh, residual, out_dtype == torch.bfloat16)
+        return ext().short_conv(x, w, bias, state, _i32(slots), _i32(lens), fresh, residual, out_dtype == torch.bfloat16, silu)
     B, S, C = x.shape
     taps = w.shape[1]
     hist = torch.zeros(B, taps - 1, C, dtype=x.dtype) if fresh else state[slots.long()]
@@ -86,6 +87,8 @@ def short_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], s
         out = out + bias
     if residual:
         out = out + x.float()
+    if silu:
+        out = F.silu(out)
     keep = torch.arange(S)[None, :] < lens[:, None]
     out = torch.where(keep[..., None], out, torch.zeros_like(out))
     if taps > 1:
@@ -314,24 +317,229 @@ def gelu_erf(x: torch.Tensor) -> torch.Tensor:
     return F.gelu(x.float()).to(x.dtype)
 
 
-def indexed_gemv(w: torch.Tensor, sel: torch.Tensor, x: torch.Tensor, gelu: bool) -> torch.Tensor:
-    """``w [E,O,I]``, ``sel [M]``, ``x [M,I]`` → ``act(w[sel[m]] @ x[m]) [M,O]`` (float accumulation)."""
+GEMV_ACTS = {None: 0, "none": 0, "gelu": 1, "silu_glu": 2}
+
+
+def indexed_gemv(w: torch.Tensor, sel: torch.Tensor, x: torch.Tensor, act) -> torch.Tensor:
+    """``w [E,O,I]``, ``sel [M]``, ``x [M,I]`` → ``act(w[sel[m]] @ x[m])`` (float accumulation).  ``act``: ``None``, ``"gelu"`` (erf
+    form; ``True`` means the same) or ``"silu_glu"``: the matrix stacks gate rows over up rows and the result is
+    ``silu(gate) * up``, ``[M, O/2]``.  Rows whose ``sel`` names no matrix (``< 0`` or ``>= E``) give zeros."""
+    kind = GEMV_ACTS["gelu" if act is True else (None if act is False else act)]
     if _cuda(x):
         _ext.count_launch()
-        return ext().indexed_gemv(w, _i32(sel), x, gelu)
-    y = torch.einsum("moi,mi->mo", w[sel.long()].float(), x.float())
-    return (F.gelu(y) if gelu else y).to(x.dtype)
+        return ext().indexed_gemv(w, _i32(sel), x, kind)
+    ok = (sel >= 0) & (sel < w.shape[0])
+    y = torch.einsum("moi,mi->mo", w[sel.long().clamp(0, w.shape[0] - 1)].float(), x.float())
+    if kind == 1:
+        y = F.gelu(y)
+    elif kind == 2:
+        half = y.shape[1] // 2
+        y = F.silu(y[:, :half]) * y[:, half:]
+    return torch.where(ok[:, None], y, torch.zeros_like(y)).to(x.dtype)
 
 
-def moe_combine(rows: torch.Tensor, src: torch.Tensor, weight: torch.Tensor, base: Optional[torch.Tensor]) -> torch.Tensor:
-    """``out[n] = base[n] + sum_k weight[n,k] * rows[src[n,k]]`` summed in float; ``rows [M,C]``, ``src, weight [N,top]``."""
+def silu_mul(gu: torch.Tensor) -> torch.Tensor:
+    """``gu [M, 2F]`` (gate columns, then up columns) → ``silu(gate) * up`` ``[M, F]``."""
+    if _cuda(gu):
+        _ext.count_launch()
+        return ext().silu_mul(gu)
+    half = gu.shape[1] // 2
+    return (F.silu(gu[:, :half].float()) * gu[:, half:].float()).to(gu.dtype)
+
+
+def moe_combine(rows: torch.Tensor, src: torch.Tensor, weight: torch.Tensor, base: Optional[torch.Tensor],
+                base_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[n] = base_weight[n] * base[n] + sum_k weight[n,k] * rows[src[n,k]]`` summed in float; ``rows [M,C]``, ``src, weight
+    [N,top]``, ``base [N,C]`` (optional; ``base_weight [N]`` float, one when absent)."""
     if _cuda(rows):
         _ext.count_launch()
-        return ext().moe_combine(rows, _i32(src), weight, base)
+        return ext().moe_combine(rows, _i32(src), weight, base, base_weight)
     y = (rows.float()[src.long()] * weight[..., None]).sum(1)
     if base is not None:
-        y = y + base.float()
+        y = y + (base.float() if base_weight is None else base.float() * base_weight[:, None])
     return y.to(rows.dtype)
+
+
+# ------------------------------------------------------------------------------------------------- embedding with sinusoid positions
+def sinusoid_inv_freq(width: int, base: float, device=None) -> torch.Tensor:
+    """``base^(-2i/width)`` for i < ceil(width/2), rounded once from float64."""
+    i = torch.arange((width + 1) // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / width).float().to(device)
+
+
+def embed_sinusoid(tokens: torch.Tensor, table: torch.Tensor, scale: float, inv_freq: torch.Tensor, pos0: torch.Tensor) -> torch.Tensor:
+    """``tokens [B,S]`` → float ``[B,S,W]``: ``table[token] * scale`` plus interleaved sinusoids of the position ``p = pos0[b] + t``
+    (coordinate 2i: ``sin(p f_i)``, 2i+1: ``cos(p f_i)``; angles in float)."""
+    if _cuda(table):
+        _ext.count_launch()
+        return ext().embed_sinusoid(tokens.contiguous(), table, float(scale), inv_freq, _i32(pos0))
+    B, S = tokens.shape
+    W = table.shape[1]
+    ang = (pos0.long()[:, None] + torch.arange(S)[None, :]).float()[..., None] * inv_freq          # [B,S,ceil(W/2)]
+    pe = torch.stack([torch.sin(ang), torch.cos(ang)], -1).reshape(B, S, -1)[..., :W]
+    return table[tokens].float() * scale + pe
+
+
+# ------------------------------------------------------------------------------------------------------------- grouped gated norm
+def group_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, groups: int, eps: float, gate_first: bool,
+                         out: Optional[torch.Tensor] = None, out_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Rows of ``x [rows, C]`` in ``groups`` equal parts, each divided by its own root mean square, with a ``silu(gate)`` factor:
+    ``gate_first``: ``rms_g(x * silu(gate)) * w`` (the gate enters the statistics); otherwise ``rms_g(x) * w * silu(gate)``.
+    ``w`` holds ``C`` numbers or ``C / groups`` (shared by the groups).  The result times ``out_scale`` goes to ``out`` (any row
+    stride) or a new ``[rows, C]`` tensor of ``out_dtype``."""
+    rows, C = x.shape
+    if out is None:
+        out = torch.empty(rows, C, dtype=out_dtype or gate.dtype, device=x.device)
+    if _cuda(x):
+        _ext.count_launch()
+        ext().group_rms_norm_gated(x, gate, w, groups, eps, gate_first, out, out_scale)
+        return out
+    xf, g = x.float(), F.silu(gate.float())
+    if gate_first:
+        xf = xf * g
+    xg = xf.view(rows, groups, C // groups)
+    y = (xg / torch.sqrt(xg.pow(2).mean(-1, keepdim=True) + eps)).view(rows, C) * (w if w.numel() == C else w.repeat(groups))
+    if not gate_first:
+        y = y * g
+    out.copy_((y * out_scale).to(out.dtype))
+    return out
+
+
+# ------------------------------------------------------------------------------------- grouped-query sliding-window attention
+def window_qk_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
+                      eps: float, pos0: torch.Tensor, lens: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor,
+                      vcache: torch.Tensor) -> None:
+    """``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views; last dim contiguous): every head's query and key is divided by its
+    root mean square and multiplied by ``qw`` / ``kw`` (``[D]`` float; ``None``: left as they are) IN PLACE; the last ``ring``
+    real tokens of each row go to ``kcache [slots, ring, G, D]`` / ``vcache [slots, ring, G, V]`` at row ``position mod ring``."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().window_qk_prepare(q, k, v, qw, kw, eps, _i32(pos0), _i32(lens), _i32(slots), kcache, vcache)
+        return
+    B, S = q.shape[:2]
+    if qw is not None:
+        qf = q.float()
+        q.copy_((qf / torch.sqrt(qf.pow(2).mean(-1, keepdim=True) + eps) * qw).to(q.dtype))
+    if kw is not None:
+        kf = k.float()
+        k.copy_((kf / torch.sqrt(kf.pow(2).mean(-1, keepdim=True) + eps) * kw).to(k.dtype))
+    ring = kcache.shape[1]
+    for b in range(B):
+        n, p0, sl = int(lens[b]), int(pos0[b]), int(slots[b])
+        for t in range(max(0, n - ring), n):
+            kcache[sl, (p0 + t) % ring] = k[b, t]
+            vcache[sl, (p0 + t) % ring] = v[b, t]
+
+
+def _capped(sc: torch.Tensor, softcap: float) -> torch.Tensor:
+    return softcap * torch.tanh(sc / softcap) if softcap > 0 else sc
+
+
+def window_attention_prompt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: Optional[torch.Tensor], lens: torch.Tensor,
+                            window: int, scale: float, softcap: float, out: torch.Tensor, out_scale: float = 1.0) -> torch.Tensor:
+    """Prompts that start at position 0: ``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views), query head h uses key/value head
+    ``h // (H/G)``; query i sees ``i - window < j <= i``.  Scores ``q.k * scale``, capped as ``softcap * tanh(score / softcap)``
+    when ``softcap > 0``, softmax in float.  Each head's result is multiplied by ``sigmoid(gate[b,s,h])`` (if given) and
+    ``out_scale`` and written to ``out [B*S, >= H*V]`` (row stride free); padded rows give zeros."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().window_attention_prompt(q, k, v, gate, _i32(lens), window, scale, softcap, out, out_scale)
+        return out
+    B, S, H, D = q.shape
+    G, V = k.shape[2], v.shape[3]
+    kk, vv = k.float().repeat_interleave(H // G, 2), v.float().repeat_interleave(H // G, 2)
+    sc = _capped(torch.einsum("bihd,bjhd->bhij", q.float(), kk) * scale, softcap)
+    i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    sc = sc.masked_fill(~((j <= i) & (j > i - window)), float("-inf"))
+    o = torch.einsum("bhij,bjhv->bihv", torch.softmax(sc, -1), vv)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())[..., None]
+    o = torch.where((torch.arange(S)[None, :] < lens[:, None])[..., None, None], o * out_scale, torch.zeros_like(o))
+    out[:, :H * V] = o.reshape(B * S, H * V).to(out.dtype)
+    return out
+
+
+def window_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, gate: Optional[torch.Tensor], slots: torch.Tensor,
+                           pos0: torch.Tensor, lens: torch.Tensor, window: int, scale: float, softcap: float, out: torch.Tensor,
+                           out_scale: float = 1.0) -> torch.Tensor:
+    """Single tokens ``q [B,1,H,D]`` at positions ``pos0`` against their slots' rings (``kcache [slots, ring, G, D]``, ``vcache
+    [slots, ring, G, V]``; row ``j mod ring`` holds position j, the token's own row included).  Same scores, gate and output
+    layout as :func:`window_attention_prompt`; rows with ``lens == 0`` give zeros."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().window_attention_token(q, kcache, vcache, gate, _i32(slots), _i32(pos0), _i32(lens), window, scale, softcap, out, out_scale)
+        return out
+    B, _, H, D = q.shape
+    ring, G, V = kcache.shape[1], kcache.shape[2], vcache.shape[3]
+    kb = kcache[slots.long()].float().repeat_interleave(H // G, 2)                                  # [B, ring, H, D]
+    vb = vcache[slots.long()].float().repeat_interleave(H // G, 2)
+    sc = _capped(torch.einsum("bhd,brhd->bhr", q[:, 0].float(), kb) * scale, softcap)
+    p = pos0.long()[:, None]
+    m = torch.remainder(p - torch.arange(ring)[None, :], ring)                                      # distance back of ring row r
+    ok = (p - m >= 0) & (m < window)
+    sc = sc.masked_fill(~ok[:, None, :], float("-inf"))
+    o = torch.einsum("bhr,brhv->bhv", torch.softmax(sc, -1), vb)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float()).view(B, H, 1)
+    o = torch.where((lens > 0)[:, None, None], o * out_scale, torch.zeros_like(o))
+    out[:, :H * V] = o.reshape(B, H * V).to(out.dtype)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- matrix-state recurrences (scalar decay)
+def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, braw: torch.Tensor, araw: torch.Tensor, a_log: torch.Tensor,
+                     dt_bias: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor, fresh: bool) -> torch.Tensor:
+    """Gated delta rule.  ``q, k [B,S,G,D]``, ``v [B,S,H,V]`` (views), ``braw, araw [B,S,H]`` float pre-activations → float
+    ``[B,S,H,V]``.  Head h reads q/k head ``h // (H/G)``; q and k are made unit vectors (``x / sqrt(sum x^2 + 1e-6)``), q also
+    times ``D^-1/2``; ``beta = sigmoid(braw)``, ``g = exp(-exp(a_log) softplus(araw + dt_bias))``; per token
+    ``M <- g M; u = beta (v - M^T k); M <- M + k u^T; o = M^T q``.  ``state [slots,H,D,V]`` float."""
+    if _cuda(q):
+        _ext.count_launch()
+        return ext().gated_delta_scan(q, k, v, braw, araw, a_log, dt_bias, state, _i32(slots), _i32(lens), fresh)
+    B, S, G, D = q.shape
+    H, V = v.shape[2], v.shape[3]
+    qf, kf = q.float(), k.float()
+    qf = (qf / torch.sqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * D ** -0.5).repeat_interleave(H // G, 2)
+    kf = (kf / torch.sqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(H // G, 2)
+    vf, beta = v.float(), torch.sigmoid(braw.float())
+    g = torch.exp(-torch.exp(a_log) * F.softplus(araw.float() + dt_bias))
+    st = torch.zeros(B, H, D, V) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, H, V)
+    for t in range(S):
+        live = (t < lens)[:, None, None, None]
+        M = g[:, t, :, None, None] * st
+        u = beta[:, t, :, None] * (vf[:, t] - torch.einsum("bhdv,bhd->bhv", M, kf[:, t]))
+        M = M + kf[:, t, :, :, None] * u[:, :, None, :]
+        st = torch.where(live, M, st)
+        out[:, t] = torch.where(live[..., 0], torch.einsum("bhdv,bhd->bhv", st, qf[:, t]), out[:, t])
+    state[slots.long()] = st
+    return out
+
+
+def ssd_scan(x: torch.Tensor, bm: torch.Tensor, cm: torch.Tensor, dtraw: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+             dskip: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor, fresh: bool) -> torch.Tensor:
+    """Selective state space recurrence with a scalar decay per head.  ``x [B,S,H,V]``, ``bm, cm [B,S,G,N]`` (views), ``dtraw
+    [B,S,H]`` float → float ``[B,S,H,V]``: ``dt = softplus(dtraw + dt_bias)``, ``M_t = exp(-exp(a_log) dt) M_(t-1) + dt b_t x_t^T``,
+    ``y_t = M_t^T c_t + dskip x_t`` with head h reading group ``h // (H/G)``.  ``state [slots,H,N,V]`` float."""
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().ssd_scan(x, bm, cm, dtraw, a_log, dt_bias, dskip, state, _i32(slots), _i32(lens), fresh)
+    B, S, H, V = x.shape
+    G, N = bm.shape[2], bm.shape[3]
+    xf = x.float()
+    bf, cf = bm.float().repeat_interleave(H // G, 2), cm.float().repeat_interleave(H // G, 2)
+    dt = F.softplus(dtraw.float() + dt_bias)
+    dec = torch.exp(-torch.exp(a_log) * dt)
+    st = torch.zeros(B, H, N, V) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, H, V)
+    for t in range(S):
+        live = (t < lens)[:, None, None, None]
+        M = dec[:, t, :, None, None] * st + (dt[:, t, :, None] * bf[:, t])[..., None] * xf[:, t, :, None, :]
+        st = torch.where(live, M, st)
+        y = torch.einsum("bhnv,bhn->bhv", st, cf[:, t]) + dskip[None, :, None] * xf[:, t]
+        out[:, t] = torch.where(live[..., 0], y, out[:, t])
+    state[slots.long()] = st
+    return out
 
 
 if __name__ == "__main__":
