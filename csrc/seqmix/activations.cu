@@ -1,9 +1,12 @@
 // Elementwise activations and the small-batch pieces of a routed feed-forward.
 //   xielu        : z > 0: ap z^2 + z/2;  z <= 0: an (exp(z) - 1 - z) + z/2   (ap, an are positive numbers prepared by the caller)
 //   gelu_erf     : 0.5 z (1 + erf(z / sqrt 2))
+//   silu_mul     : silu(gate) * up for rows [gate | up]
 //   indexed_gemv : out[m,:] = act(W[sel[m]] x[m,:]) for a few rows m, each with its own matrix out of a stack [E, O, I]
-//                  (token generation: the chosen experts' matrices are streamed once, a warp per output row)
-//   moe_combine  : y[n,:] = base[n,:] + sum_k weight[n,k] * rows[src[n,k],:], summed in float
+//                  (token generation: the chosen experts' matrices are streamed once, a warp per output row); act 0: none,
+//                  1: gelu_erf, 2: the matrix stacks gate rows over up rows and out = silu(gate row . x) * (up row . x), O/2 columns;
+//                  rows whose sel names no matrix give zeros
+//   moe_combine  : y[n,:] = base_weight[n] * base[n,:] + sum_k weight[n,k] * rows[src[n,k],:], summed in float
 #include "seq_common.cuh"
 #include "seqmix.h"
 
@@ -44,12 +47,7 @@ static void act_launch(const void* x, void* out, long n, float ap, float an, cud
 }
 
 template <typename T, bool VEC>
-__global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restrict__ sel, const T* __restrict__ x, long x_stride,
-                                    int M, int O, int I, int act, T* __restrict__ out) {
-    const int o = blockIdx.x * blockDim.y + threadIdx.y, m = blockIdx.y, lane = threadIdx.x;
-    if (o >= O) return;
-    const T* wr = w + ((long)sel[m] * O + o) * I;
-    const T* xr = x + (long)m * x_stride;
+__device__ __forceinline__ float row_dot(const T* __restrict__ wr, const T* __restrict__ xr, int I, int lane) {
     float acc = 0.f;
     if (VEC) {                                   // four weights per lane and access, two accesses in flight
         float acc2 = 0.f;
@@ -67,16 +65,45 @@ __global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restri
     } else {
         for (int i = lane; i < I; i += 32) acc = fmaf(ldf(wr + i), ldf(xr + i), acc);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) stf(out + (long)m * O + o, act ? gelu_erf_(acc) : acc);
+    return warp_sum(acc);
+}
+
+template <typename T, bool VEC>
+__global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restrict__ sel, const T* __restrict__ x, long x_stride,
+                                    int M, int E, int O, int I, int act, T* __restrict__ out) {
+    const int On = act == 2 ? O / 2 : O;
+    const int o = blockIdx.x * blockDim.y + threadIdx.y, m = blockIdx.y, lane = threadIdx.x;
+    if (o >= On) return;
+    const int e = sel[m];
+    if (e < 0 || e >= E) {
+        if (lane == 0) stf(out + (long)m * On + o, 0.f);
+        return;
+    }
+    const T* wr = w + ((long)e * O + o) * I;
+    const T* xr = x + (long)m * x_stride;
+    float acc = row_dot<T, VEC>(wr, xr, I, lane);
+    if (act == 1) acc = gelu_erf_(acc);
+    else if (act == 2) acc = acc * sigmoidf_(acc) * row_dot<T, VEC>(wr + (long)On * I, xr, I, lane);
+    if (lane == 0) stf(out + (long)m * On + o, acc);
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, long rows, int F, T* __restrict__ out) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * F) return;
+    const long r = i / F;
+    const int c = (int)(i - r * F);
+    const float g = ldf(gu + r * 2 * F + c), u = ldf(gu + r * 2 * F + F + c);
+    stf(out + i, g * sigmoidf_(g) * u);
 }
 
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ src, const float* __restrict__ weight,
-                                   const T* __restrict__ base, int N, int top, int C, T* __restrict__ out) {
+                                   const T* __restrict__ base, const float* __restrict__ base_weight, int N, int top, int C,
+                                   T* __restrict__ out) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x, n = blockIdx.y;
     if (c >= C) return;
-    float acc = base ? ldf(base + (long)n * C + c) : 0.f;
+    float acc = base ? ldf(base + (long)n * C + c) * (base_weight ? base_weight[n] : 1.f) : 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(weight[(long)n * top + k], ldf(rows + (long)src[(long)n * top + k] * C + c), acc);
     stf(out + (long)n * C + c, acc);
 }
@@ -91,13 +118,21 @@ void gelu_erf(const void* x, void* out, int bf, long n, cudaStream_t s) {
     if (bf) act_launch<bf16, 1>(x, out, n, 0.f, 0.f, s); else act_launch<float, 1>(x, out, n, 0.f, 0.f, s);
 }
 
-void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int O, int I, int act, void* out,
+void silu_mul(const void* gu, void* out, int bf, long rows, int F, cudaStream_t s) {
+    if (rows * F == 0) return;
+    const unsigned blocks = (unsigned)((rows * F + 255) / 256);
+    if (bf) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, rows, F, (bf16*)out);
+    else silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, rows, F, (float*)out);
+}
+
+void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int E, int O, int I, int act, void* out,
                   cudaStream_t s) {
     if (M == 0) return;
-    dim3 block(32, 8), grid((O + 7) / 8, M);
+    const int On = act == 2 ? O / 2 : O;
+    dim3 block(32, 8), grid((On + 7) / 8, M);
     const size_t a4 = bf ? 8 : 16;
     const bool vec = I % 4 == 0 && x_stride % 4 == 0 && (uintptr_t)w % a4 == 0 && (uintptr_t)x % a4 == 0;
-#define SEQMIX_IGEMV(T, V) indexed_gemv_kernel<T, V><<<grid, block, 0, s>>>((const T*)w, sel, (const T*)x, x_stride, M, O, I, act, (T*)out)
+#define SEQMIX_IGEMV(T, V) indexed_gemv_kernel<T, V><<<grid, block, 0, s>>>((const T*)w, sel, (const T*)x, x_stride, M, E, O, I, act, (T*)out)
     if (bf) { if (vec) SEQMIX_IGEMV(bf16, true); else SEQMIX_IGEMV(bf16, false); }
     else { if (vec) SEQMIX_IGEMV(float, true); else SEQMIX_IGEMV(float, false); }
 #undef SEQMIX_IGEMV
@@ -106,10 +141,12 @@ void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_s
 // four columns per thread (C and the bases in whole fours)
 template <typename T>
 __global__ void moe_combine_vec_kernel(const T* __restrict__ rows, const int* __restrict__ src, const float* __restrict__ weight,
-                                       const T* __restrict__ base, int N, int top, int C, T* __restrict__ out) {
+                                       const T* __restrict__ base, const float* __restrict__ base_weight, int N, int top, int C,
+                                       T* __restrict__ out) {
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4, n = blockIdx.y;
     if (c >= C) return;
     float4 acc = base ? ld4(base + (long)n * C + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (base && base_weight) { const float bw = base_weight[n]; acc.x *= bw; acc.y *= bw; acc.z *= bw; acc.w *= bw; }
     for (int k = 0; k < top; ++k) {
         const float w = weight[(long)n * top + k];
         const float4 r = ld4(rows + (long)src[(long)n * top + k] * C + c);
@@ -118,19 +155,19 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ rows, const int* __
     st4(out + (long)n * C + c, acc);
 }
 
-void moe_combine(const void* rows, const int* src, const float* weight, const void* base, int bf, int N, int top, int C, void* out,
-                 cudaStream_t s) {
+void moe_combine(const void* rows, const int* src, const float* weight, const void* base, const float* base_weight, int bf, int N, int top,
+                 int C, void* out, cudaStream_t s) {
     if (N == 0) return;
     const size_t a4 = bf ? 8 : 16;
     if (C % 4 == 0 && (uintptr_t)rows % a4 == 0 && (uintptr_t)out % a4 == 0 && (base == nullptr || (uintptr_t)base % a4 == 0)) {
         dim3 vblock(128), vgrid((C / 4 + 127) / 128, N);
-        if (bf) moe_combine_vec_kernel<bf16><<<vgrid, vblock, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, N, top, C, (bf16*)out);
-        else moe_combine_vec_kernel<float><<<vgrid, vblock, 0, s>>>((const float*)rows, src, weight, (const float*)base, N, top, C, (float*)out);
+        if (bf) moe_combine_vec_kernel<bf16><<<vgrid, vblock, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, base_weight, N, top, C, (bf16*)out);
+        else moe_combine_vec_kernel<float><<<vgrid, vblock, 0, s>>>((const float*)rows, src, weight, (const float*)base, base_weight, N, top, C, (float*)out);
         return;
     }
     dim3 block(128), grid((C + 127) / 128, N);
-    if (bf) moe_combine_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, N, top, C, (bf16*)out);
-    else moe_combine_kernel<float><<<grid, block, 0, s>>>((const float*)rows, src, weight, (const float*)base, N, top, C, (float*)out);
+    if (bf) moe_combine_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)rows, src, weight, (const bf16*)base, base_weight, N, top, C, (bf16*)out);
+    else moe_combine_kernel<float><<<grid, block, 0, s>>>((const float*)rows, src, weight, (const float*)base, base_weight, N, top, C, (float*)out);
 }
 
 }  // namespace seqmix

@@ -1,0 +1,78 @@
+// Python bindings of the grouped-query sliding-window attention kernels.
+#include "bind_common.h"
+
+static const float* opt_f32(const c10::optional<Tensor>& t) { return t ? f32(*t) : nullptr; }
+
+// q [B,S,H,D], k [B,S,G,D], v [B,S,G,V] (views; last dim contiguous, heads one after another); caches [slots, ring, G, D|V]
+void window_qk_prepare(Tensor q, Tensor k, const Tensor& v, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, double eps,
+                       const Tensor& pos0, const Tensor& lens, const Tensor& slots, Tensor kcache, Tensor vcache) {
+    TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1,
+                "bad attention operands");
+    const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), G = k.size(2), V = v.size(3);
+    TORCH_CHECK(k.size(3) == D && v.size(2) == G && H % G == 0 && (H == 1 || q.stride(2) == D) && (G == 1 || (k.stride(2) == D && v.stride(2) == V)),
+                "heads must be laid out one after another");
+    TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() && kcache.scalar_type() == q.scalar_type() &&
+                    vcache.scalar_type() == q.scalar_type(), "dtype mismatch");
+    TORCH_CHECK(kcache.is_contiguous() && vcache.is_contiguous() && kcache.dim() == 4 && vcache.dim() == 4 && kcache.size(1) == vcache.size(1) &&
+                    kcache.size(2) == G && kcache.size(3) == D && vcache.size(2) == G && vcache.size(3) == V, "caches must be [slots, ring, G, D|V]");
+    TORCH_CHECK((!qw || qw->numel() == D) && (!kw || kw->numel() == D), "norm weights must hold D numbers");
+    seqmix::window_qk_prepare(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
+                              v.stride(1), is_bf(q), opt_f32(qw), opt_f32(kw), (float)eps, i32(pos0), i32(lens), i32(slots), kcache.data_ptr(),
+                              vcache.data_ptr(), (int)kcache.size(1), B, S, H, G, D, V, stream());
+    check_launch();
+}
+
+static void check_out(const Tensor& out, long rows, long cols, const Tensor& like) {
+    TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == rows && out.size(1) >= cols && out.stride(1) == 1 &&
+                    out.scalar_type() == like.scalar_type(), "out must be [rows, >= heads * vdim] of the activations' dtype");
+}
+
+void window_attention_prompt(const Tensor& q, const Tensor& k, const Tensor& v, const c10::optional<Tensor>& gate, const Tensor& lens,
+                             int64_t window, double scale, double softcap, Tensor out, double out_scale) {
+    TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1,
+                "bad attention operands");
+    const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), G = k.size(2), V = v.size(3);
+    TORCH_CHECK(k.size(3) == D && v.size(2) == G && H % G == 0 && (H == 1 || q.stride(2) == D) && (G == 1 || (k.stride(2) == D && v.stride(2) == V)),
+                "heads must be laid out one after another");
+    TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "dtype mismatch");
+    check_out(out, (long)B * S, (long)H * V, q);
+    const void* gp = nullptr;
+    long g_sb = 0, g_st = 0;
+    if (gate) {
+        TORCH_CHECK(gate->dim() == 3 && gate->size(2) == H && gate->stride(2) == 1 && gate->scalar_type() == q.scalar_type(), "gate must be [B,S,H]");
+        gp = gate->data_ptr(); g_sb = gate->stride(0); g_st = gate->stride(1);
+    }
+    bool ok = seqmix::window_attention_prompt(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(),
+                                              v.stride(0), v.stride(1), gp, g_sb, g_st, is_bf(q), i32(lens), B, S, H, G, D, V, (int)window,
+                                              (float)scale, (float)softcap, out.data_ptr(), out.stride(0), (float)out_scale, stream());
+    TORCH_CHECK(ok, "window_attention_prompt: sizes do not fit the kernel (vdim <= 256)");
+    check_launch();
+}
+
+void window_attention_token(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const c10::optional<Tensor>& gate, const Tensor& slots,
+                            const Tensor& pos0, const Tensor& lens, int64_t window, double scale, double softcap, Tensor out,
+                            double out_scale) {
+    TORCH_CHECK(q.is_cuda() && q.dim() == 4 && q.size(1) == 1 && q.stride(3) == 1 && kcache.dim() == 4 && vcache.dim() == 4 &&
+                    kcache.is_contiguous() && vcache.is_contiguous(), "bad attention operands");
+    const int B = q.size(0), H = q.size(2), D = q.size(3), G = kcache.size(2), V = vcache.size(3), ring = kcache.size(1);
+    TORCH_CHECK(kcache.size(3) == D && vcache.size(2) == G && vcache.size(1) == ring && H % G == 0 && (H == 1 || q.stride(2) == D), "shape mismatch");
+    TORCH_CHECK(q.scalar_type() == kcache.scalar_type() && q.scalar_type() == vcache.scalar_type(), "dtype mismatch");
+    check_out(out, B, (long)H * V, q);
+    const void* gp = nullptr;
+    long g_sb = 0;
+    if (gate) {
+        TORCH_CHECK(gate->dim() == 3 && gate->size(2) == H && gate->stride(2) == 1 && gate->scalar_type() == q.scalar_type(), "gate must be [B,1,H]");
+        gp = gate->data_ptr(); g_sb = gate->stride(0);
+    }
+    bool ok = seqmix::window_attention_token(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), gp, g_sb, is_bf(q), i32(slots),
+                                             i32(pos0), i32(lens), ring, B, H, G, D, V, (int)window, (float)scale, (float)softcap,
+                                             out.data_ptr(), out.stride(0), (float)out_scale, stream());
+    TORCH_CHECK(ok, "window_attention_token: sizes do not fit the kernel (vdim <= 256)");
+    check_launch();
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("window_qk_prepare", &window_qk_prepare);
+    m.def("window_attention_prompt", &window_attention_prompt);
+    m.def("window_attention_token", &window_attention_token);
+}

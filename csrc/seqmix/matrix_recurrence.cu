@@ -1,0 +1,234 @@
+// Recurrences with a matrix state per head and ONE decay per head and token, states in float.
+//   gated_delta_scan : M <- g M;  u = beta (v - M^T k);  M <- M + k u^T;  o = M^T q      (M [D, V]; the read-out sees the write)
+//                      q and k are made unit vectors here (x / sqrt(sum x^2 + 1e-6), q also times D^-1/2); beta = sigmoid(braw),
+//                      g = exp(-exp(a_log) softplus(araw + dt_bias)).  With A = M_old^T k and Bq = M_old^T q one pass over the old
+//                      state gives u = beta (v - g A) and o = g Bq + (k.q) u, and the update M = g M_old + k u^T follows in registers.
+//   ssd_scan         : dt = softplus(dtraw + dt_bias);  M <- exp(-exp(a_log) dt) M + dt b x^T;  y = M^T c + dskip x   (M [N, V])
+// A block owns 32 value columns of one (sequence, head): lane = column, warp = one of 8 row groups, a thread keeps rows
+// r, r + 8, ... of its column in registers, so state loads and stores are whole 128-byte rows.  Tokens are staged through shared
+// memory 8 at a time (a warp prepares one token: norms, decays, gates); the per-token sums over rows are folded across the warps
+// through a double-buffered shared array (one barrier per token).  Tokens at or past lens[b] write zeros and leave the state alone.
+#include "seq_common.cuh"
+#include "seqmix.h"
+
+namespace seqmix {
+
+constexpr int kCols = 32, kRowGroups = 8, kTok = 8;
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(256) gated_delta_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, long qk_sb, long qk_st, const T* __restrict__ v, long v_sb, long v_st,
+    const float* __restrict__ braw, const float* __restrict__ araw, long ba_sb, long ba_st, const float* __restrict__ a_log,
+    const float* __restrict__ dt_bias, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int S,
+    int H, int G, int D, int V, float qscale, float* __restrict__ out) {
+    extern __shared__ float sm[];
+    float* sk = sm;                              // [kTok][D] unit keys
+    float* sq = sk + kTok * D;                   // [kTok][D] unit queries times qscale
+    float* sv = sq + kTok * D;                   // [kTok][kCols]
+    float* sc = sv + kTok * kCols;               // [kTok][4]: g, beta, k.q
+    float* part = sc + kTok * 4;                 // [2][2][kRowGroups][kCols]
+    const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
+    const int lane = threadIdx.x & 31, r = threadIdx.x >> 5, j = j0 + lane;
+    const int len = min(lens[b], S), hk = h / (H / G);
+    const bool col = j < V;
+    float* sp = state + (((long)slots[b] * H + h) * D) * V;
+    float M[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r + i * kRowGroups;
+        M[i] = (!fresh && col && d < D) ? sp[(long)d * V + j] : 0.f;
+    }
+    const float ea = expf(a_log[h]), db = dt_bias[h];
+    for (int t0 = 0; t0 < len; t0 += kTok) {
+        __syncthreads();                         // the previous chunk's tokens are consumed
+        {                                        // warp r prepares token t0 + r
+            const int t = t0 + r;
+            if (t < len) {
+                const T* qp = q + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+                const T* kp = k + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+                float qq = 0.f, kk = 0.f, qk = 0.f;
+                for (int d = lane; d < D; d += 32) {
+                    const float a = ldf(qp + d), c = ldf(kp + d);
+                    qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); qk = fmaf(a, c, qk);
+                    sq[r * D + d] = a; sk[r * D + d] = c;
+                }
+                qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+                const float iq = qscale / sqrtf(qq + 1e-6f), ik = 1.f / sqrtf(kk + 1e-6f);
+                for (int d = lane; d < D; d += 32) { sq[r * D + d] *= iq; sk[r * D + d] *= ik; }
+                sv[r * kCols + lane] = col ? ldf(v + (long)b * v_sb + (long)t * v_st + (long)h * V + j) : 0.f;
+                if (lane == 0) {
+                    const long o = (long)b * ba_sb + (long)t * ba_st + h;
+                    sc[r * 4 + 0] = expf(-ea * softplusf_(araw[o] + db));
+                    sc[r * 4 + 1] = sigmoidf_(braw[o]);
+                    sc[r * 4 + 2] = qk * iq * ik;
+                }
+            }
+        }
+        __syncthreads();
+        const int nt = min(kTok, len - t0);
+        for (int u = 0; u < nt; ++u) {
+            const float* ku = sk + u * D;
+            const float* qu = sq + u * D;
+            float A = 0.f, Bq = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = r + i * kRowGroups;
+                if (d < D) { A = fmaf(M[i], ku[d], A); Bq = fmaf(M[i], qu[d], Bq); }
+            }
+            float* pb = part + ((t0 + u) & 1) * 2 * kRowGroups * kCols;
+            pb[r * kCols + lane] = A;
+            pb[(kRowGroups + r) * kCols + lane] = Bq;
+            __syncthreads();
+            A = 0.f; Bq = 0.f;
+#pragma unroll
+            for (int w = 0; w < kRowGroups; ++w) { A += pb[w * kCols + lane]; Bq += pb[(kRowGroups + w) * kCols + lane]; }
+            const float g = sc[u * 4], beta = sc[u * 4 + 1], kq = sc[u * 4 + 2];
+            const float uv = beta * (sv[u * kCols + lane] - g * A);
+            if (r == 0 && col) out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(g, Bq, kq * uv);
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = r + i * kRowGroups;
+                if (d < D) M[i] = fmaf(g, M[i], ku[d] * uv);
+            }
+        }
+    }
+    if (col) {
+        for (int t = len + r; t < S; t += kRowGroups) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = r + i * kRowGroups;
+            if (d < D && (len > 0 || fresh)) sp[(long)d * V + j] = M[i];
+        }
+    }
+}
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(256) ssd_kernel(
+    const T* __restrict__ x, long x_sb, long x_st, const T* __restrict__ bm, const T* __restrict__ cm, long bc_sb, long bc_st,
+    const float* __restrict__ dtraw, long dt_sb, long dt_st, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ dskip, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int S, int H,
+    int G, int N, int V, float* __restrict__ out) {
+    extern __shared__ float sm[];
+    float* sb = sm;                              // [kTok][N] dt * b
+    float* scm = sb + kTok * N;                  // [kTok][N] c
+    float* sx = scm + kTok * N;                  // [kTok][kCols]
+    float* sc = sx + kTok * kCols;               // [kTok][2]: decay
+    float* part = sc + kTok * 2;                 // [2][kRowGroups][kCols]
+    const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
+    const int lane = threadIdx.x & 31, r = threadIdx.x >> 5, j = j0 + lane;
+    const int len = min(lens[b], S), hg = h / (H / G);
+    const bool col = j < V;
+    float* sp = state + (((long)slots[b] * H + h) * N) * V;
+    float M[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r + i * kRowGroups;
+        M[i] = (!fresh && col && d < N) ? sp[(long)d * V + j] : 0.f;
+    }
+    const float ea = expf(a_log[h]), db = dt_bias[h], ds = dskip[h];
+    for (int t0 = 0; t0 < len; t0 += kTok) {
+        __syncthreads();
+        {
+            const int t = t0 + r;
+            if (t < len) {
+                const float dt = softplusf_(dtraw[(long)b * dt_sb + (long)t * dt_st + h] + db);
+                const T* bp = bm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
+                const T* cp = cm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
+                for (int d = lane; d < N; d += 32) { sb[r * N + d] = dt * ldf(bp + d); scm[r * N + d] = ldf(cp + d); }
+                sx[r * kCols + lane] = col ? ldf(x + (long)b * x_sb + (long)t * x_st + (long)h * V + j) : 0.f;
+                if (lane == 0) sc[r * 2] = expf(-ea * dt);
+            }
+        }
+        __syncthreads();
+        const int nt = min(kTok, len - t0);
+        for (int u = 0; u < nt; ++u) {
+            const float* bu = sb + u * N;
+            const float* cu = scm + u * N;
+            const float dec = sc[u * 2], xv = sx[u * kCols + lane];
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = r + i * kRowGroups;
+                if (d < N) { M[i] = fmaf(dec, M[i], bu[d] * xv); y = fmaf(M[i], cu[d], y); }
+            }
+            float* pb = part + ((t0 + u) & 1) * kRowGroups * kCols;
+            pb[r * kCols + lane] = y;
+            __syncthreads();
+            if (r == 0 && col) {
+                y = 0.f;
+#pragma unroll
+                for (int w = 0; w < kRowGroups; ++w) y += pb[w * kCols + lane];
+                out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(ds, xv, y);
+            }
+        }
+    }
+    if (col) {
+        for (int t = len + r; t < S; t += kRowGroups) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = r + i * kRowGroups;
+            if (d < N && (len > 0 || fresh)) sp[(long)d * V + j] = M[i];
+        }
+    }
+}
+
+static int rows_per_thread(int D) {
+    const int need = (D + kRowGroups - 1) / kRowGroups;
+    for (int p = 1; p <= 64; p *= 2)
+        if (need <= p) return p;
+    return 0;
+}
+
+bool gated_delta_scan(const void* q, const void* k, long qk_sb, long qk_st, const void* v, long v_sb, long v_st, int bf, const float* braw,
+                      const float* araw, long ba_sb, long ba_st, const float* a_log, const float* dt_bias, float* state, const int* slots,
+                      const int* lens, int fresh, int B, int S, int H, int G, int D, int V, float qscale, float* out, cudaStream_t s) {
+    const int dpt = rows_per_thread(D);
+    if (!dpt) return false;
+    if (B == 0 || S == 0) return true;
+    dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
+    const size_t smem = sizeof(float) * (2 * kTok * D + kTok * kCols + kTok * 4 + 2 * 2 * kRowGroups * kCols);
+#define SEQMIX_GDR(T, P)                                                                                                              \
+    gated_delta_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, (const T*)k, qk_sb, qk_st, (const T*)v, v_sb, v_st, braw, araw, ba_sb, \
+                                                       ba_st, a_log, dt_bias, state, slots, lens, fresh, S, H, G, D, V, qscale, out)
+#define SEQMIX_GDR_T(P) do { if (bf) SEQMIX_GDR(bf16, P); else SEQMIX_GDR(float, P); } while (0)
+    switch (dpt) {
+        case 1: SEQMIX_GDR_T(1); break;
+        case 2: SEQMIX_GDR_T(2); break;
+        case 4: SEQMIX_GDR_T(4); break;
+        case 8: SEQMIX_GDR_T(8); break;
+        case 16: SEQMIX_GDR_T(16); break;
+        case 32: SEQMIX_GDR_T(32); break;
+        default: SEQMIX_GDR_T(64); break;
+    }
+#undef SEQMIX_GDR_T
+#undef SEQMIX_GDR
+    return true;
+}
+
+bool ssd_scan(const void* x, long x_sb, long x_st, const void* bm, const void* cm, long bc_sb, long bc_st, int bf, const float* dtraw,
+              long dt_sb, long dt_st, const float* a_log, const float* dt_bias, const float* dskip, float* state, const int* slots,
+              const int* lens, int fresh, int B, int S, int H, int G, int N, int V, float* out, cudaStream_t s) {
+    const int dpt = rows_per_thread(N);
+    if (!dpt) return false;
+    if (B == 0 || S == 0) return true;
+    dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
+    const size_t smem = sizeof(float) * (2 * kTok * N + kTok * kCols + kTok * 2 + 2 * kRowGroups * kCols);
+#define SEQMIX_SSD(T, P)                                                                                                              \
+    ssd_kernel<T, P><<<grid, block, smem, s>>>((const T*)x, x_sb, x_st, (const T*)bm, (const T*)cm, bc_sb, bc_st, dtraw, dt_sb, dt_st,   \
+                                               a_log, dt_bias, dskip, state, slots, lens, fresh, S, H, G, N, V, out)
+#define SEQMIX_SSD_T(P) do { if (bf) SEQMIX_SSD(bf16, P); else SEQMIX_SSD(float, P); } while (0)
+    switch (dpt) {
+        case 1: SEQMIX_SSD_T(1); break;
+        case 2: SEQMIX_SSD_T(2); break;
+        case 4: SEQMIX_SSD_T(4); break;
+        case 8: SEQMIX_SSD_T(8); break;
+        case 16: SEQMIX_SSD_T(16); break;
+        case 32: SEQMIX_SSD_T(32); break;
+        default: SEQMIX_SSD_T(64); break;
+    }
+#undef SEQMIX_SSD_T
+#undef SEQMIX_SSD
+    return true;
+}
+
+}  // namespace seqmix

@@ -62,6 +62,48 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int ro
     }
 }
 
+// Rows in `groups` equal parts, each part divided by its own root mean square; a warp per (row, part).  gate_first: the statistics
+// are those of x * silu(gate); otherwise silu(gate) multiplies the normed values.  w holds C numbers or C / groups (wn says which).
+template <typename Tin, typename Tg>
+__global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_stride, const Tg* __restrict__ gate, long gate_stride,
+                                            const float* __restrict__ w, int wn, int rows, int C, int groups, float eps, int gate_first,
+                                            Tg* __restrict__ out, long out_stride, float out_scale) {
+    const long unit = (long)blockIdx.x * blockDim.y + threadIdx.y;
+    if (unit >= (long)rows * groups) return;
+    const int row = (int)(unit / groups), g = (int)(unit - (long)row * groups), Cg = C / groups, lane = threadIdx.x;
+    const Tin* xr = x + (long)row * x_stride + (long)g * Cg;
+    const Tg* gr = gate + (long)row * gate_stride + (long)g * Cg;
+    float ss = 0.f;
+    for (int c = lane; c < Cg; c += 32) {
+        float v = ldf(xr + c);
+        if (gate_first) { const float z = ldf(gr + c); v *= z * sigmoidf_(z); }
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = out_scale / sqrtf(warp_sum(ss) / (float)Cg + eps);
+    const float* wr = w + (wn == C ? (long)g * Cg : 0);
+    Tg* o = out + (long)row * out_stride + (long)g * Cg;
+    for (int c = lane; c < Cg; c += 32) {
+        const float z = ldf(gr + c);
+        stf(o + c, ldf(xr + c) * (z * sigmoidf_(z)) * inv * wr[c]);
+    }
+}
+
+void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,
+                          int wn, int rows, int C, int groups, float eps, int gate_first, void* out, long out_stride, float out_scale,
+                          cudaStream_t s) {
+    const long units = (long)rows * groups;
+    if (units == 0) return;
+    dim3 block(32, 8), grid((unsigned)((units + 7) / 8));
+#define SEQMIX_GN(TI, TG)                                                                                                             \
+    group_rms_norm_gated_kernel<TI, TG><<<grid, block, 0, s>>>((const TI*)x, x_stride, (const TG*)gate, gate_stride, w, wn, rows, C, groups, \
+                                                               eps, gate_first, (TG*)out, out_stride, out_scale)
+    if (in_bf16 && gate_bf16) SEQMIX_GN(bf16, bf16);
+    else if (!in_bf16 && gate_bf16) SEQMIX_GN(float, bf16);
+    else if (!in_bf16 && !gate_bf16) SEQMIX_GN(float, float);
+    else SEQMIX_GN(bf16, float);
+#undef SEQMIX_GN
+}
+
 void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const float* w, int w_stride, float eps, const void* gate,
               long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, cudaStream_t s) {
     const bool few = rows < 148 * 8 && C >= 512;

@@ -5,7 +5,7 @@
 namespace seqmix {
 
 void short_conv(const void* x, int in_bf16, long x_sb, long x_st, const float* w, const float* bias, void* state, const int* slots,
-                const int* lens, int B, int S, int C, int taps, int fresh, int residual, void* out, int out_bf16, cudaStream_t s);
+                const int* lens, int B, int S, int C, int taps, int fresh, int residual, int act, void* out, int out_bf16, cudaStream_t s);
 void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const float* w, int w_stride, float eps, const void* gate,
               long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, cudaStream_t s);
 void latent_kv_store(const void* kv, int bf, long kv_sb, long kv_st, int B, int S, int C, int R, int dims, const float* nw, float eps,
@@ -50,9 +50,33 @@ void rglru_scan(const void* u, int bf, const float* gr, const float* gi, int wb,
                 int B, int S, int W, void* out, cudaStream_t s);
 void xielu(const void* x, void* out, int bf, long n, float ap, float an, cudaStream_t s);
 void gelu_erf(const void* x, void* out, int bf, long n, cudaStream_t s);
-void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int O, int I, int act, void* out,
+void silu_mul(const void* gu, void* out, int bf, long rows, int F, cudaStream_t s);
+// act 0: none, 1: gelu_erf, 2: silu(gate rows . x) * (up rows . x) with the gate rows stacked over the up rows (O/2 outputs)
+void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int E, int O, int I, int act, void* out,
                   cudaStream_t s);
-void moe_combine(const void* rows, const int* src, const float* weight, const void* base, int bf, int N, int top, int C, void* out,
-                 cudaStream_t s);
+void moe_combine(const void* rows, const int* src, const float* weight, const void* base, const float* base_weight, int bf, int N, int top,
+                 int C, void* out, cudaStream_t s);
+void embed_sinusoid(const long* tokens, const void* table, int bf, float scale, const float* inv_freq, const int* pos0, int B, int S, int W,
+                    int vocab, float* out, cudaStream_t s);
+void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,
+                          int wn, int rows, int C, int groups, float eps, int gate_first, void* out, long out_stride, float out_scale,
+                          cudaStream_t s);
+// Grouped-query sliding-window attention (window_attention.cu); false: sizes do not fit (value size above 256).
+void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st, int bf,
+                       const float* qw, const float* kw, float eps, const int* pos0, const int* lens, const int* slots, void* kcache,
+                       void* vcache, int ring, int B, int S, int H, int G, int D, int V, cudaStream_t s);
+bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
+                             const void* gate, long g_sb, long g_st, int bf, const int* lens, int B, int S, int H, int G, int D, int V,
+                             int window, float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s);
+bool window_attention_token(const void* q, long q_sb, const void* kcache, const void* vcache, const void* gate, long g_sb, int bf,
+                            const int* slots, const int* pos0, const int* lens, int ring, int B, int H, int G, int D, int V, int window,
+                            float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s);
+// Matrix-state recurrences with one decay per head and token (matrix_recurrence.cu); false: the state has too many rows.
+bool gated_delta_scan(const void* q, const void* k, long qk_sb, long qk_st, const void* v, long v_sb, long v_st, int bf, const float* braw,
+                      const float* araw, long ba_sb, long ba_st, const float* a_log, const float* dt_bias, float* state, const int* slots,
+                      const int* lens, int fresh, int B, int S, int H, int G, int D, int V, float qscale, float* out, cudaStream_t s);
+bool ssd_scan(const void* x, long x_sb, long x_st, const void* bm, const void* cm, long bc_sb, long bc_st, int bf, const float* dtraw,
+              long dt_sb, long dt_st, const float* a_log, const float* dt_bias, const float* dskip, float* state, const int* slots,
+              const int* lens, int fresh, int B, int S, int H, int G, int N, int V, float* out, cudaStream_t s);
 
 }  // namespace seqmix

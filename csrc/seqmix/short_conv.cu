@@ -13,7 +13,7 @@ constexpr int kMaxTaps = 16;
 template <typename Tin, typename Tout>
 __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_st, const float* __restrict__ w,
                                   const float* __restrict__ bias, Tin* state, const int* __restrict__ slots,
-                                  const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual,
+                                  const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual, int act,
                                   Tout* __restrict__ out) {
     const int c = blockIdx.x * 32 + threadIdx.x, b = blockIdx.y;
     const int len = min(lens[b], S);
@@ -40,6 +40,7 @@ __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_s
                     }
                 }
                 if (residual) acc += ldf(xb + (long)t * x_st + c);
+                if (act) acc *= sigmoidf_(acc);
             }
             stf(out + ((long)b * S + t) * C + c, acc);
         }
@@ -71,7 +72,7 @@ constexpr int kVecTaps = 8, kRun = 8;
 template <typename Tin, typename Tout, int VT>
 __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long x_st, const float* __restrict__ w,
                                       const float* __restrict__ bias, Tin* state, const int* __restrict__ slots,
-                                      const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual,
+                                      const int* __restrict__ lens, int S, int C, int taps, int fresh, int residual, int act,
                                       Tout* __restrict__ out) {
     const int c = (blockIdx.x * 32 + threadIdx.x) * 4, b = blockIdx.z, tbase = blockIdx.y * (kRun * 8) + threadIdx.y * kRun;
     const int len = min(lens[b], S), hist = taps - 1;
@@ -116,6 +117,7 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
                     acc.x = fmaf(wl.x, cur.x, acc.x); acc.y = fmaf(wl.y, cur.y, acc.y);
                     acc.z = fmaf(wl.z, cur.z, acc.z); acc.w = fmaf(wl.w, cur.w, acc.w);
                     if (residual) { acc.x += cur.x; acc.y += cur.y; acc.z += cur.z; acc.w += cur.w; }
+                    if (act) { acc.x *= sigmoidf_(acc.x); acc.y *= sigmoidf_(acc.y); acc.z *= sigmoidf_(acc.z); acc.w *= sigmoidf_(acc.w); }
                 }
                 st4(out + ((long)b * S + t) * C + c, acc);
 #pragma unroll
@@ -138,31 +140,31 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
 
 template <typename Tin, typename Tout>
 static void launch(const void* x, long x_sb, long x_st, const float* w, const float* bias, void* state, const int* slots,
-                   const int* lens, int B, int S, int C, int taps, int fresh, int residual, void* out, cudaStream_t s) {
+                   const int* lens, int B, int S, int C, int taps, int fresh, int residual, int act, void* out, cudaStream_t s) {
     const bool vec = taps <= kVecTaps && C % 4 == 0 && x_sb % 4 == 0 && x_st % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                      (uintptr_t)state % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0);
     if (vec) {
         dim3 grid((C / 4 + 31) / 32, (S + kRun * 8 - 1) / (kRun * 8), B), block(32, 8);
         if (taps <= 4)
             short_conv_vec_kernel<Tin, Tout, 4><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
-                                                                      fresh, residual, (Tout*)out);
+                                                                      fresh, residual, act, (Tout*)out);
         else
             short_conv_vec_kernel<Tin, Tout, 8><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
-                                                                      fresh, residual, (Tout*)out);
+                                                                      fresh, residual, act, (Tout*)out);
         return;
     }
     int ty = S >= 16 ? 16 : (S >= 4 ? 4 : 1);
     dim3 grid((C + 31) / 32, B), block(32, ty);
     short_conv_kernel<Tin, Tout><<<grid, block, 0, s>>>((const Tin*)x, x_sb, x_st, w, bias, (Tin*)state, slots, lens, S, C, taps,
-                                                       fresh, residual, (Tout*)out);
+                                                       fresh, residual, act, (Tout*)out);
 }
 
 void short_conv(const void* x, int in_bf16, long x_sb, long x_st, const float* w, const float* bias, void* state, const int* slots,
-                const int* lens, int B, int S, int C, int taps, int fresh, int residual, void* out, int out_bf16, cudaStream_t s) {
-    if (in_bf16 && out_bf16) launch<bf16, bf16>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, out, s);
-    else if (!in_bf16 && out_bf16) launch<float, bf16>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, out, s);
-    else if (!in_bf16 && !out_bf16) launch<float, float>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, out, s);
-    else launch<bf16, float>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, out, s);
+                const int* lens, int B, int S, int C, int taps, int fresh, int residual, int act, void* out, int out_bf16, cudaStream_t s) {
+    if (in_bf16 && out_bf16) launch<bf16, bf16>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, act, out, s);
+    else if (!in_bf16 && out_bf16) launch<float, bf16>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, act, out, s);
+    else if (!in_bf16 && !out_bf16) launch<float, float>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, act, out, s);
+    else launch<bf16, float>(x, x_sb, x_st, w, bias, state, slots, lens, B, S, C, taps, fresh, residual, act, out, s);
 }
 
 }  // namespace seqmix

@@ -1,0 +1,339 @@
+// Grouped-query softmax attention over a sliding window (no positional rotation): query position i sees i - window < j <= i;
+// query head h reads key/value head h / (H/G).  Scores are q.k * scale, capped as softcap * tanh(score / softcap) when softcap > 0;
+// scores, softmax weights and sums are float.  Each head's result may be multiplied by sigmoid(gate[b,t,h]) and a constant before
+// it is written (row stride free: several mixers write side by side into one buffer).
+//   window_qk_prepare      : RMS norm per head of queries and keys in place (one weight vector each), and the last `ring` real
+//                            tokens' keys and values to the sequence's ring rows (position mod ring)
+//   window_attention_prompt: prompts starting at position 0, keys and values of the call itself.  A block owns 16 consecutive
+//                            queries of one head (4 warps x 4 queries); key / value rows come through shared memory 32 at a time;
+//                            in the score pass a lane owns one key (4 queries per shared-memory read), in the value pass a lane
+//                            owns value columns lane, lane + 32, ...
+//   window_attention_token : one query per (sequence, head) against the ring.  A block owns one (sequence, head); its 4 warps take
+//                            ring chunks of 32 rows in turn (each through its own shared-memory buffer) and their partial softmaxes
+//                            are merged at the end.
+#include <math.h>
+
+#include "seq_common.cuh"
+#include "seqmix.h"
+
+namespace seqmix {
+
+template <typename T>
+__global__ void window_qk_prepare_kernel(T* q, long q_sb, long q_st, T* k, long k_sb, long k_st, const T* __restrict__ v, long v_sb,
+                                         long v_st, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                         const int* __restrict__ pos0, const int* __restrict__ lens, const int* __restrict__ slots,
+                                         T* kcache, T* vcache, int ring, int S, int H, int G, int D, int V) {
+    const int row = blockIdx.x, b = row / S, t = row - b * S, lane = threadIdx.x;
+    const int len = min(lens[b], S);
+    if (t >= len) return;
+    const bool keep = t >= len - ring;
+    const long cr = ((long)slots[b] * ring + (pos0[b] + t) % ring) * G;
+    for (int u = threadIdx.y; u < H + 2 * G; u += blockDim.y) {
+        if (u < H + G) {
+            const bool isq = u < H;
+            const int hh = isq ? u : u - H;
+            T* p = isq ? q + (long)b * q_sb + (long)t * q_st + (long)hh * D : k + (long)b * k_sb + (long)t * k_st + (long)hh * D;
+            const float* w = isq ? qw : kw;
+            T* dst = (!isq && keep) ? kcache + (cr + hh) * D : nullptr;
+            float inv = 1.f;
+            if (w) {
+                float ss = 0.f;
+                for (int d = lane; d < D; d += 32) { const float x = ldf(p + d); ss = fmaf(x, x, ss); }
+                inv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+            }
+            if (w || dst) {
+                for (int d = lane; d < D; d += 32) {
+                    const float x = w ? ldf(p + d) * inv * w[d] : ldf(p + d);
+                    if (w) stf(p + d, x);
+                    if (dst) stf(dst + d, x);
+                }
+            }
+        } else if (keep) {
+            const int hh = u - H - G;
+            const T* p = v + (long)b * v_sb + (long)t * v_st + (long)hh * V;
+            T* dst = vcache + (cr + hh) * V;
+            for (int d = lane; d < V; d += 32) dst[d] = p[d];
+        }
+    }
+}
+
+__device__ __forceinline__ float cap_score(float s, float softcap, float inv_cap) { return softcap > 0.f ? softcap * tanhf(s * inv_cap) : s; }
+
+constexpr int kKeys = 32;       // keys per shared-memory chunk
+constexpr int kQW = 4;          // queries per warp (prompts)
+constexpr int kWarps = 4;
+
+// shared: Ks [kKeys][D+1], Vs [kKeys][V], Qs [kWarps][D][kQW], Ps [kWarps][kKeys][kQW]
+template <typename T, int VPL>
+__global__ void __launch_bounds__(128) window_prompt_kernel(
+    const T* __restrict__ q, long q_sb, long q_st, const T* __restrict__ k, long k_sb, long k_st, const T* __restrict__ v, long v_sb,
+    long v_st, const T* __restrict__ gate, long g_sb, long g_st, const int* __restrict__ lens, int S, int H, int G, int D, int V,
+    int window, float scale, float softcap, T* __restrict__ out, long out_stride, float out_scale) {
+    extern __shared__ float sm[];
+    const int DP = D + 1;
+    float* Ks = sm;
+    float* Vs = Ks + kKeys * DP;
+    float* Qs = Vs + kKeys * V;
+    float* Ps = Qs + kWarps * D * kQW;
+    const int i0 = blockIdx.x * (kWarps * kQW), h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int len = min(lens[b], S);
+    const int iq0 = i0 + wp * kQW;                                   // this warp's first query position
+    float* Qw = Qs + wp * D * kQW;
+    float* Pw = Ps + wp * kKeys * kQW;
+    for (int x = lane; x < D * kQW; x += 32) {
+        const int d = x / kQW, rq = x - d * kQW, i = iq0 + rq;
+        Qw[x] = i < len ? ldf(q + (long)b * q_sb + (long)i * q_st + (long)h * D + d) : 0.f;
+    }
+    float m[kQW], l[kQW], acc[kQW][VPL];
+#pragma unroll
+    for (int rq = 0; rq < kQW; ++rq) {
+        m[rq] = -INFINITY; l[rq] = 0.f;
+#pragma unroll
+        for (int c = 0; c < VPL; ++c) acc[rq][c] = 0.f;
+    }
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const int last = min(i0 + kWarps * kQW, len) - 1;                // last key any query of the block sees
+    const int first = max(0, i0 - window + 1);
+    const T* kb = k + (long)b * k_sb + (long)g * D;
+    const T* vb = v + (long)b * v_sb + (long)g * V;
+    for (int c0 = first; c0 <= last; c0 += kKeys) {
+        __syncthreads();
+        for (int x = tid; x < kKeys * D; x += 128) {
+            const int jj = x / D, d = x - jj * D, j = c0 + jj;
+            Ks[jj * DP + d] = j <= last ? ldf(kb + (long)j * k_st + d) : 0.f;
+        }
+        for (int x = tid; x < kKeys * V; x += 128) {
+            const int jj = x / V, d = x - jj * V, j = c0 + jj;
+            Vs[x] = j <= last ? ldf(vb + (long)j * v_st + d) : 0.f;
+        }
+        __syncthreads();
+        // is any of this warp's queries inside the chunk's reach?
+        if (c0 > iq0 + kQW - 1 || c0 + kKeys - 1 <= iq0 - window || iq0 >= len) continue;
+        float s[kQW];
+#pragma unroll
+        for (int rq = 0; rq < kQW; ++rq) s[rq] = 0.f;
+        const float* kr = Ks + lane * DP;
+        for (int d = 0; d < D; ++d) {
+            const float kv = kr[d];
+            const float4 qv = *reinterpret_cast<const float4*>(Qw + d * kQW);
+            s[0] = fmaf(qv.x, kv, s[0]); s[1] = fmaf(qv.y, kv, s[1]); s[2] = fmaf(qv.z, kv, s[2]); s[3] = fmaf(qv.w, kv, s[3]);
+        }
+        const int j = c0 + lane;
+        float corr[kQW];
+#pragma unroll
+        for (int rq = 0; rq < kQW; ++rq) {
+            const int i = iq0 + rq;
+            const bool ok = i < len && j <= i && j > i - window;
+            const float sc = ok ? cap_score(s[rq] * scale, softcap, inv_cap) : -INFINITY;
+            float mx = sc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float mn = fmaxf(m[rq], mx);
+            const float p = (ok && mn > -INFINITY) ? expf(sc - mn) : 0.f;
+            corr[rq] = (m[rq] > -INFINITY) ? expf(m[rq] - mn) : 0.f;
+            m[rq] = mn;
+            l[rq] = fmaf(l[rq], corr[rq], p);                        // per-lane part of the sum; folded at the end
+            Pw[lane * kQW + rq] = p;
+        }
+#pragma unroll
+        for (int rq = 0; rq < kQW; ++rq)
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) acc[rq][c] *= corr[rq];
+        __syncwarp();
+        for (int jj = 0; jj < kKeys; ++jj) {
+            const float4 p = *reinterpret_cast<const float4*>(Pw + jj * kQW);
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) {
+                const int col = lane + 32 * c;
+                const float vv = col < V ? Vs[jj * V + col] : 0.f;
+                acc[0][c] = fmaf(p.x, vv, acc[0][c]); acc[1][c] = fmaf(p.y, vv, acc[1][c]);
+                acc[2][c] = fmaf(p.z, vv, acc[2][c]); acc[3][c] = fmaf(p.w, vv, acc[3][c]);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int rq = 0; rq < kQW; ++rq) {
+        const int i = iq0 + rq;
+        if (i >= S) continue;
+        const float lt = warp_sum(l[rq]);
+        float f = 0.f;
+        if (i < len && lt > 0.f) {
+            f = out_scale / lt;
+            if (gate) f *= sigmoidf_(ldf(gate + (long)b * g_sb + (long)i * g_st + h));
+        }
+        T* o = out + ((long)b * S + i) * out_stride + (long)h * V;
+#pragma unroll
+        for (int c = 0; c < VPL; ++c) {
+            const int col = lane + 32 * c;
+            if (col < V) stf(o + col, acc[rq][c] * f);
+        }
+    }
+}
+
+// shared per warp: Ks [kKeys][D+1], Vs [kKeys][V], Qs [D], Ps [kKeys]; then the merge area [kWarps][2 + 32*VPL]
+template <typename T, int VPL>
+__global__ void __launch_bounds__(128) window_token_kernel(
+    const T* __restrict__ q, long q_sb, const T* __restrict__ kcache, const T* __restrict__ vcache, const T* __restrict__ gate, long g_sb,
+    const int* __restrict__ slots, const int* __restrict__ pos0, const int* __restrict__ lens, int ring, int H, int G, int D, int V,
+    int window, float scale, float softcap, T* __restrict__ out, long out_stride, float out_scale) {
+    extern __shared__ float sm[];
+    const int DP = D + 1, per = kKeys * DP + kKeys * V + D + kKeys;
+    const int h = blockIdx.x, b = blockIdx.y, g = h / (H / G);
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    float* Ks = sm + wp * per;
+    float* Vs = Ks + kKeys * DP;
+    float* Qw = Vs + kKeys * V;
+    float* Pw = Qw + D;
+    float* mg = sm + kWarps * per;
+    T* o = out + (long)b * out_stride + (long)h * V;
+    if (lens[b] <= 0) {
+        for (int c = tid; c < V; c += 128) stf(o + c, 0.f);
+        return;
+    }
+    const int p = pos0[b];
+    for (int d = lane; d < D; d += 32) Qw[d] = ldf(q + (long)b * q_sb + (long)h * D + d);
+    __syncwarp();
+    float m = -INFINITY, l = 0.f, acc[VPL];
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const T* kb = kcache + (long)slots[b] * ring * G * D + (long)g * D;
+    const T* vb = vcache + (long)slots[b] * ring * G * V + (long)g * V;
+    const int rows = min(ring, p + 1);                               // ring rows that hold a position (rows 0..p before the ring wraps)
+    for (int c0 = wp * kKeys; c0 < rows; c0 += kWarps * kKeys) {
+        for (int x = lane; x < kKeys * D; x += 32) {
+            const int jj = x / D, d = x - jj * D, rr = c0 + jj;
+            Ks[jj * DP + d] = rr < rows ? ldf(kb + (long)rr * G * D + d) : 0.f;
+        }
+        for (int x = lane; x < kKeys * V; x += 32) {
+            const int jj = x / V, d = x - jj * V, rr = c0 + jj;
+            Vs[x] = rr < rows ? ldf(vb + (long)rr * G * V + d) : 0.f;
+        }
+        __syncwarp();
+        float s = 0.f;
+        const float* kr = Ks + lane * DP;
+        for (int d = 0; d < D; ++d) s = fmaf(Qw[d], kr[d], s);
+        const int rr = c0 + lane;
+        int back = (p - rr) % ring;                                  // how far back the position of ring row rr lies
+        if (back < 0) back += ring;
+        const bool ok = rr < rows && back < window && p - back >= 0;
+        const float sc = ok ? cap_score(s * scale, softcap, inv_cap) : -INFINITY;
+        float mx = sc;
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+        const float mn = fmaxf(m, mx);
+        const float pr = (ok && mn > -INFINITY) ? expf(sc - mn) : 0.f;
+        const float corr = (m > -INFINITY) ? expf(m - mn) : 0.f;
+        m = mn;
+        l = fmaf(l, corr, pr);
+        Pw[lane] = pr;
+#pragma unroll
+        for (int c = 0; c < VPL; ++c) acc[c] *= corr;
+        __syncwarp();
+        for (int jj = 0; jj < kKeys; ++jj) {
+            const float pj = Pw[jj];
+#pragma unroll
+            for (int c = 0; c < VPL; ++c) {
+                const int col = lane + 32 * c;
+                acc[c] = fmaf(pj, col < V ? Vs[jj * V + col] : 0.f, acc[c]);
+            }
+        }
+        __syncwarp();
+    }
+    l = warp_sum(l);
+    float* mw = mg + wp * (2 + 32 * VPL);
+    if (lane == 0) { mw[0] = m; mw[1] = l; }
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) mw[2 + c * 32 + lane] = acc[c];
+    __syncthreads();
+    if (wp != 0) return;
+    float mt = -INFINITY;
+    for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, mg[w * (2 + 32 * VPL)]);
+    float lt = 0.f;
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
+    for (int w = 0; w < kWarps; ++w) {
+        const float* x = mg + w * (2 + 32 * VPL);
+        if (x[0] == -INFINITY) continue;
+        const float f = expf(x[0] - mt);
+        lt = fmaf(x[1], f, lt);
+#pragma unroll
+        for (int c = 0; c < VPL; ++c) acc[c] = fmaf(x[2 + c * 32 + lane], f, acc[c]);
+    }
+    float f = lt > 0.f ? out_scale / lt : 0.f;
+    if (gate) f *= sigmoidf_(ldf(gate + (long)b * g_sb + h));
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+        const int col = lane + 32 * c;
+        if (col < V) stf(o + col, acc[c] * f);
+    }
+}
+
+void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st, int bf,
+                       const float* qw, const float* kw, float eps, const int* pos0, const int* lens, const int* slots, void* kcache,
+                       void* vcache, int ring, int B, int S, int H, int G, int D, int V, cudaStream_t s) {
+    if (B * S == 0) return;
+    dim3 grid(B * S), block(32, 8);
+    if (bf)
+        window_qk_prepare_kernel<bf16><<<grid, block, 0, s>>>((bf16*)q, q_sb, q_st, (bf16*)k, k_sb, k_st, (const bf16*)v, v_sb, v_st, qw, kw, eps,
+                                                             pos0, lens, slots, (bf16*)kcache, (bf16*)vcache, ring, S, H, G, D, V);
+    else
+        window_qk_prepare_kernel<float><<<grid, block, 0, s>>>((float*)q, q_sb, q_st, (float*)k, k_sb, k_st, (const float*)v, v_sb, v_st, qw, kw,
+                                                              eps, pos0, lens, slots, (float*)kcache, (float*)vcache, ring, S, H, G, D, V);
+}
+
+static int value_cols_per_lane(int V) { return V <= 64 ? 2 : (V <= 128 ? 4 : (V <= 256 ? 8 : 0)); }
+
+template <typename K>
+static bool raise_smem(K kernel, size_t smem) {
+    if (smem <= 48 * 1024) return true;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+}
+
+bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
+                             const void* gate, long g_sb, long g_st, int bf, const int* lens, int B, int S, int H, int G, int D, int V,
+                             int window, float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s) {
+    const int vpl = value_cols_per_lane(V);
+    if (!vpl) return false;
+    if (B * S == 0) return true;
+    const size_t smem = sizeof(float) * ((size_t)kKeys * (D + 1) + (size_t)kKeys * V + (size_t)kWarps * D * kQW + kWarps * kKeys * kQW);
+    dim3 grid((S + kWarps * kQW - 1) / (kWarps * kQW), H, B), block(128);
+#define SEQMIX_WP(T, P)                                                                                                               \
+    do {                                                                                                                              \
+        if (!raise_smem(window_prompt_kernel<T, P>, smem)) return false;                                                              \
+        window_prompt_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, q_sb, q_st, (const T*)k, k_sb, k_st, (const T*)v, v_sb, v_st,   \
+                                                             (const T*)gate, g_sb, g_st, lens, S, H, G, D, V, window, scale, softcap,   \
+                                                             (T*)out, out_stride, out_scale);                                         \
+    } while (0)
+#define SEQMIX_WP_T(P) do { if (bf) SEQMIX_WP(bf16, P); else SEQMIX_WP(float, P); } while (0)
+    if (vpl == 2) SEQMIX_WP_T(2); else if (vpl == 4) SEQMIX_WP_T(4); else SEQMIX_WP_T(8);
+#undef SEQMIX_WP_T
+#undef SEQMIX_WP
+    return true;
+}
+
+bool window_attention_token(const void* q, long q_sb, const void* kcache, const void* vcache, const void* gate, long g_sb, int bf,
+                            const int* slots, const int* pos0, const int* lens, int ring, int B, int H, int G, int D, int V, int window,
+                            float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s) {
+    const int vpl = value_cols_per_lane(V);
+    if (!vpl) return false;
+    if (B == 0) return true;
+    const size_t smem = sizeof(float) * ((size_t)kWarps * (kKeys * (D + 1) + kKeys * V + D + kKeys) + kWarps * (2 + 32 * vpl));
+    dim3 grid(H, B), block(128);
+#define SEQMIX_WT(T, P)                                                                                                               \
+    do {                                                                                                                              \
+        if (!raise_smem(window_token_kernel<T, P>, smem)) return false;                                                               \
+        window_token_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, q_sb, (const T*)kcache, (const T*)vcache, (const T*)gate, g_sb,  \
+                                                            slots, pos0, lens, ring, H, G, D, V, window, scale, softcap, (T*)out,      \
+                                                            out_stride, out_scale);                                                   \
+    } while (0)
+#define SEQMIX_WT_T(P) do { if (bf) SEQMIX_WT(bf16, P); else SEQMIX_WT(float, P); } while (0)
+    if (vpl == 2) SEQMIX_WT_T(2); else if (vpl == 4) SEQMIX_WT_T(4); else SEQMIX_WT_T(8);
+#undef SEQMIX_WT_T
+#undef SEQMIX_WT
+    return true;
+}
+
+}  // namespace seqmix

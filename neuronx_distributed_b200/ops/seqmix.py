@@ -2,8 +2,8 @@
 float residual stream), latent sliding-window attention over a ring cache, gated linear recurrences (per-key-channel decay; real-gated
 LRU), xIELU / erf-GELU and the small-batch pieces of a routed feed-forward.
 
-CUDA tensors run the hand-written kernels of ``csrc/seqmix`` (extension ``nxd_b200_seq_C``, built in-tree on first use so that a
-fresh checkout compiles only these few files); CPU tensors run the plain PyTorch statements below, which define the semantics.
+CUDA tensors run the hand-written kernels of ``csrc/seqmix`` (one small extension per kernel group, built in-tree on first use so
+that a fresh checkout compiles only the files of the mechanisms its model has); CPU tensors run the plain PyTorch statements below, which define the semantics.
 Conventions: activations are ``[B, S, ...]`` right-padded batches with ``lens [B]`` (int32) real tokens per row; ``slots [B]``
 (int32) names each row's block in a state tensor; ``fresh`` means the rows start a sequence in this call (history / state = 0).
 Everything the kernels keep in float (statistics, scores, decays, states) is float here as well."""
@@ -22,43 +22,86 @@ import torch.nn.functional as F
 
 from . import _ext
 
-EXT_NAME = "nxd_b200_seq_C"
 SEQ_BUILD_DIR = _ext.BUILD_DIR / "seqmix"
 CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
-_C = None
+
+# Kernel groups, each its own extension ``nxd_b200_seq_<group>_C`` built in-tree on first use, so that a model compiles only the
+# mechanisms it has: group → (sources, functions it exports).
+GROUPS = {
+    "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "bind_core.cpp"],
+             ["short_conv", "rms_norm", "add_rms_norm_", "xielu", "gelu_erf", "silu_mul", "indexed_gemv", "moe_combine", "embed_sinusoid",
+              "group_rms_norm_gated"]),
+    "latent": (["latent_attention.cu", "latent_decode.cu", "latent_prefill.cu", "bind_latent.cpp"],
+               ["latent_kv_store", "rope_q_", "latent_window_attention", "window_softmax", "latent_prompt_attention",
+                "latent_prompt_attention_fits"]),
+    "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan"]),
+    "window": (["window_attention.cu", "bind_window.cpp"], ["window_qk_prepare", "window_attention_prompt", "window_attention_token"]),
+    "matrec": (["matrix_recurrence.cu", "bind_matrec.cpp"], ["gated_delta_scan", "ssd_scan"]),
+}
+_GROUP_OF = {fn: g for g, (_, fns) in GROUPS.items() for fn in fns}
+_MODS = {}
 
 
-def build(verbose: bool = False) -> Path:
-    """Compile ``csrc/seqmix`` for sm_100a into ``_build/seqmix`` (IEEE math: no fast-math, the float paths are exact-rounded)."""
+def ext_name(group: str) -> str:
+    return f"nxd_b200_seq_{group}_C"
+
+
+def build_group(group: str, verbose: bool = False) -> Path:
+    """Compile one kernel group for sm_100a into ``_build/seqmix/<group>`` (IEEE math: no fast-math, the float paths are
+    exact-rounded)."""
     from torch.utils import cpp_extension
 
-    SEQ_BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    out = SEQ_BUILD_DIR / group
+    out.mkdir(parents=True, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
     os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
-    srcs = sorted(str(p) for p in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
-    cpp_extension.load(name=EXT_NAME, sources=srcs, extra_cflags=["-O3", "-std=c++17"],
+    srcs = [str(CSRC / f) for f in GROUPS[group][0]]
+    cpp_extension.load(name=ext_name(group), sources=srcs, extra_cflags=["-O3", "-std=c++17"],
                        extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
                                           "--expt-relaxed-constexpr"],
-                       extra_include_paths=[str(CSRC)], build_directory=str(SEQ_BUILD_DIR), verbose=verbose, is_python_module=True,
+                       extra_include_paths=[str(CSRC)], build_directory=str(out), verbose=verbose, is_python_module=True,
                        with_cuda=True)
-    so = SEQ_BUILD_DIR / f"{EXT_NAME}.so"
+    so = out / f"{ext_name(group)}.so"
     assert so.exists(), f"build did not produce {so}"
     return so
 
 
-def ext():
-    """The extension module; built on first use when absent (needs nvcc, no GPU)."""
-    global _C
-    if _C is None:
-        so = SEQ_BUILD_DIR / f"{EXT_NAME}.so"
-        if not so.exists():
-            build()
-        loader = importlib.machinery.ExtensionFileLoader(EXT_NAME, str(so))
-        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(EXT_NAME, loader))
+def build(verbose: bool = False):
+    """Compile every kernel group; returns the built libraries."""
+    return [build_group(g, verbose) for g in GROUPS]
+
+
+def _group_module(group: str):
+    """A group's extension module; built on first use when absent or older than its sources (needs nvcc, no GPU)."""
+    if group not in _MODS:
+        so = SEQ_BUILD_DIR / group / f"{ext_name(group)}.so"
+        deps = [CSRC / f for f in GROUPS[group][0]] + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh"))
+        if not so.exists() or so.stat().st_mtime < max(p.stat().st_mtime for p in deps):
+            build_group(group)
+        loader = importlib.machinery.ExtensionFileLoader(ext_name(group), str(so))
+        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(ext_name(group), loader))
         loader.exec_module(mod)
-        sys.modules[EXT_NAME] = mod
-        _C = mod
-    return _C
+        sys.modules[ext_name(group)] = mod
+        _MODS[group] = mod
+    return _MODS[group]
+
+
+class _Kernels:
+    """``ext().name`` → the function ``name`` of whichever group exports it."""
+
+    def __getattr__(self, name: str):
+        if name not in _GROUP_OF:
+            raise AttributeError(name)
+        fn = getattr(_group_module(_GROUP_OF[name]), name)
+        setattr(self, name, fn)
+        return fn
+
+
+_KERNELS = _Kernels()
+
+
+def ext():
+    return _KERNELS
 
 
 def _cuda(t: torch.Tensor) -> bool:
@@ -543,4 +586,5 @@ def ssd_scan(x: torch.Tensor, bm: torch.Tensor, cm: torch.Tensor, dtraw: torch.T
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv))
+    for _so in build(verbose="-v" in sys.argv):
+        print(_so)
