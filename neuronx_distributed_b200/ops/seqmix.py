@@ -521,6 +521,7 @@ def window_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
     m = torch.remainder(p - torch.arange(ring)[None, :], ring)                                      # distance back of ring row r
     ok = (p - m >= 0) & (m < window)
     sc = sc.masked_fill(~ok[:, None, :], float("-inf"))
+    vb = torch.where(ok[:, :, None, None], vb, torch.zeros_like(vb))                               # rows never written hold anything
     o = torch.einsum("bhr,brhv->bhv", torch.softmax(sc, -1), vb)
     if gate is not None:
         o = o * torch.sigmoid(gate.float()).view(B, H, 1)

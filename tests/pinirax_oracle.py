@@ -68,7 +68,8 @@ def window_attention(h, P, m, eps):
         for hd in range(H):
             g = hd // (H // G)
             sc = (k[lo:i + 1, g] @ q[i, hd]) * scale
-            sc = cap * torch.tanh(sc / cap)
+            if cap > 0:                                                    # a cap of zero stands for no cap
+                sc = cap * torch.tanh(sc / cap)
             p = torch.softmax(sc, 0)
             out[i, hd] = (p[:, None] * v[lo:i + 1, g]).sum(0) * gate[i, hd]
     return out.reshape(S, H * V) @ P["o"].T
