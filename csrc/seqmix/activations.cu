@@ -118,8 +118,25 @@ void gelu_erf(const void* x, void* out, int bf, long n, cudaStream_t s) {
     if (bf) act_launch<bf16, 1>(x, out, n, 0.f, 0.f, s); else act_launch<float, 1>(x, out, n, 0.f, 0.f, s);
 }
 
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, long rows, int F, T* __restrict__ out) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= rows * F) return;
+    const long r = i / F;
+    const int c = (int)(i - r * F);
+    const float4 g = ld4(gu + r * 2 * F + c), u = ld4(gu + r * 2 * F + F + c);
+    st4(out + i, make_float4(g.x * sigmoidf_(g.x) * u.x, g.y * sigmoidf_(g.y) * u.y, g.z * sigmoidf_(g.z) * u.z, g.w * sigmoidf_(g.w) * u.w));
+}
+
 void silu_mul(const void* gu, void* out, int bf, long rows, int F, cudaStream_t s) {
     if (rows * F == 0) return;
+    const size_t a4 = bf ? 8 : 16;
+    if (F % 4 == 0 && (uintptr_t)gu % a4 == 0 && (uintptr_t)out % a4 == 0) {
+        const unsigned vblocks = (unsigned)((rows * F / 4 + 255) / 256);
+        if (bf) silu_mul_vec_kernel<bf16><<<vblocks, 256, 0, s>>>((const bf16*)gu, rows, F, (bf16*)out);
+        else silu_mul_vec_kernel<float><<<vblocks, 256, 0, s>>>((const float*)gu, rows, F, (float*)out);
+        return;
+    }
     const unsigned blocks = (unsigned)((rows * F + 255) / 256);
     if (bf) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, rows, F, (bf16*)out);
     else silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, rows, F, (float*)out);

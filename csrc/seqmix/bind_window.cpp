@@ -64,9 +64,13 @@ void window_attention_token(const Tensor& q, const Tensor& kcache, const Tensor&
         TORCH_CHECK(gate->dim() == 3 && gate->size(2) == H && gate->stride(2) == 1 && gate->scalar_type() == q.scalar_type(), "gate must be [B,1,H]");
         gp = gate->data_ptr(); g_sb = gate->stride(0);
     }
+    const int splits = seqmix::window_token_splits(ring, B, H, G);
+    const auto f = q.options().dtype(at::kFloat);
+    Tensor pm = at::empty({B, H, splits}, f), pl = at::empty({B, H, splits}, f), pa = at::empty({B, H, splits, V}, f);
     bool ok = seqmix::window_attention_token(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(), gp, g_sb, is_bf(q), i32(slots),
-                                             i32(pos0), i32(lens), ring, B, H, G, D, V, (int)window, (float)scale, (float)softcap,
-                                             out.data_ptr(), out.stride(0), (float)out_scale, stream());
+                                             i32(pos0), i32(lens), ring, B, H, G, D, V, (int)window, (float)scale, (float)softcap, splits,
+                                             pm.data_ptr<float>(), pl.data_ptr<float>(), pa.data_ptr<float>(), out.data_ptr(),
+                                             out.stride(0), (float)out_scale, stream());
     TORCH_CHECK(ok, "window_attention_token: sizes do not fit the kernel (vdim <= 256)");
     check_launch();
 }

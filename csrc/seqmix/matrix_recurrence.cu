@@ -6,7 +6,8 @@
 //   ssd_scan         : dt = softplus(dtraw + dt_bias);  M <- exp(-exp(a_log) dt) M + dt b x^T;  y = M^T c + dskip x   (M [N, V])
 // A block owns 32 value columns of one (sequence, head): lane = column, warp = one of 8 row groups, a thread keeps rows
 // r, r + 8, ... of its column in registers, so state loads and stores are whole 128-byte rows.  Tokens are staged through shared
-// memory 8 at a time (a warp prepares one token: norms, decays, gates); the per-token sums over rows are folded across the warps
+// memory 8 at a time (a warp prepares one token: norms, decays, gates, from numbers fetched one chunk ahead); the per-token sums over
+// rows are folded across the warps
 // through a double-buffered shared array (one barrier per token).  Tokens at or past lens[b] write zeros and leave the state alone.
 #include "seq_common.cuh"
 #include "seqmix.h"
@@ -39,32 +40,49 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
         M[i] = (!fresh && col && d < D) ? sp[(long)d * V + j] : 0.f;
     }
     const float ea = expf(a_log[h]), db = dt_bias[h];
+    // warp r prepares token t0 + r of every chunk; its raw numbers are fetched one chunk ahead, so that the loads fly during the
+    // previous chunk's arithmetic
+    constexpr int DL = DPT >= 4 ? DPT / 4 : 1;   // key coordinates per lane: D <= 8 DPT = 32 DL
+    float qraw[DL], kraw[DL], vraw = 0.f, braw_ = 0.f, araw_ = 0.f;
+    auto fetch = [&](int t) {
+        if (t < len) {
+            const T* qp = q + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+            const T* kp = k + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                qraw[i] = d < D ? ldf(qp + d) : 0.f;
+                kraw[i] = d < D ? ldf(kp + d) : 0.f;
+            }
+            vraw = col ? ldf(v + (long)b * v_sb + (long)t * v_st + (long)h * V + j) : 0.f;
+            const long o = (long)b * ba_sb + (long)t * ba_st + h;
+            braw_ = braw[o];
+            araw_ = araw[o];
+        }
+    };
+    fetch(r);
     for (int t0 = 0; t0 < len; t0 += kTok) {
         __syncthreads();                         // the previous chunk's tokens are consumed
-        {                                        // warp r prepares token t0 + r
-            const int t = t0 + r;
-            if (t < len) {
-                const T* qp = q + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
-                const T* kp = k + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
-                float qq = 0.f, kk = 0.f, qk = 0.f;
-                for (int d = lane; d < D; d += 32) {
-                    const float a = ldf(qp + d), c = ldf(kp + d);
-                    qq = fmaf(a, a, qq); kk = fmaf(c, c, kk); qk = fmaf(a, c, qk);
-                    sq[r * D + d] = a; sk[r * D + d] = c;
-                }
-                qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
-                const float iq = qscale / sqrtf(qq + 1e-6f), ik = 1.f / sqrtf(kk + 1e-6f);
-                for (int d = lane; d < D; d += 32) { sq[r * D + d] *= iq; sk[r * D + d] *= ik; }
-                sv[r * kCols + lane] = col ? ldf(v + (long)b * v_sb + (long)t * v_st + (long)h * V + j) : 0.f;
-                if (lane == 0) {
-                    const long o = (long)b * ba_sb + (long)t * ba_st + h;
-                    sc[r * 4 + 0] = expf(-ea * softplusf_(araw[o] + db));
-                    sc[r * 4 + 1] = sigmoidf_(braw[o]);
-                    sc[r * 4 + 2] = qk * iq * ik;
-                }
+        if (t0 + r < len) {
+            float qq = 0.f, kk = 0.f, qk = 0.f;
+#pragma unroll
+            for (int i = 0; i < DL; ++i) { qq = fmaf(qraw[i], qraw[i], qq); kk = fmaf(kraw[i], kraw[i], kk); qk = fmaf(qraw[i], kraw[i], qk); }
+            qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+            const float iq = qscale / sqrtf(qq + 1e-6f), ik = 1.f / sqrtf(kk + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) { sq[r * D + d] = qraw[i] * iq; sk[r * D + d] = kraw[i] * ik; }
+            }
+            sv[r * kCols + lane] = vraw;
+            if (lane == 0) {
+                sc[r * 4 + 0] = expf(-ea * softplusf_(araw_ + db));
+                sc[r * 4 + 1] = sigmoidf_(braw_);
+                sc[r * 4 + 2] = qk * iq * ik;
             }
         }
         __syncthreads();
+        fetch(t0 + kTok + r);
         const int nt = min(kTok, len - t0);
         for (int u = 0; u < nt; ++u) {
             const float* ku = sk + u * D;
@@ -126,20 +144,37 @@ __global__ void __launch_bounds__(256) ssd_kernel(
         M[i] = (!fresh && col && d < N) ? sp[(long)d * V + j] : 0.f;
     }
     const float ea = expf(a_log[h]), db = dt_bias[h], ds = dskip[h];
+    constexpr int DL = DPT >= 4 ? DPT / 4 : 1;   // state rows per lane when a warp prepares a token: N <= 8 DPT = 32 DL
+    float braw[DL], craw[DL], xraw = 0.f, dtr = 0.f;
+    auto fetch = [&](int t) {
+        if (t < len) {
+            const T* bp = bm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
+            const T* cp = cm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                braw[i] = d < N ? ldf(bp + d) : 0.f;
+                craw[i] = d < N ? ldf(cp + d) : 0.f;
+            }
+            xraw = col ? ldf(x + (long)b * x_sb + (long)t * x_st + (long)h * V + j) : 0.f;
+            dtr = dtraw[(long)b * dt_sb + (long)t * dt_st + h];
+        }
+    };
+    fetch(r);
     for (int t0 = 0; t0 < len; t0 += kTok) {
         __syncthreads();
-        {
-            const int t = t0 + r;
-            if (t < len) {
-                const float dt = softplusf_(dtraw[(long)b * dt_sb + (long)t * dt_st + h] + db);
-                const T* bp = bm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
-                const T* cp = cm + (long)b * bc_sb + (long)t * bc_st + (long)hg * N;
-                for (int d = lane; d < N; d += 32) { sb[r * N + d] = dt * ldf(bp + d); scm[r * N + d] = ldf(cp + d); }
-                sx[r * kCols + lane] = col ? ldf(x + (long)b * x_sb + (long)t * x_st + (long)h * V + j) : 0.f;
-                if (lane == 0) sc[r * 2] = expf(-ea * dt);
+        if (t0 + r < len) {
+            const float dt = softplusf_(dtr + db);
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < N) { sb[r * N + d] = dt * braw[i]; scm[r * N + d] = craw[i]; }
             }
+            sx[r * kCols + lane] = xraw;
+            if (lane == 0) sc[r * 2] = expf(-ea * dt);
         }
         __syncthreads();
+        fetch(t0 + kTok + r);
         const int nt = min(kTok, len - t0);
         for (int u = 0; u < nt; ++u) {
             const float* bu = sb + u * N;

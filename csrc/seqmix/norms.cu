@@ -62,27 +62,60 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int ro
     }
 }
 
-// Rows in `groups` equal parts, each part divided by its own root mean square; a warp per (row, part).  gate_first: the statistics
-// are those of x * silu(gate); otherwise silu(gate) multiplies the normed values.  w holds C numbers or C / groups (wn says which).
-template <typename Tin, typename Tg>
+// Rows in `groups` equal parts, each part divided by its own root mean square.  blockDim.x threads share a (row, part) unit (32: a
+// warp per unit; 256: a block per unit, for long parts), blockDim.y units per block.  gate_first: the statistics are those of
+// x * silu(gate); otherwise silu(gate) multiplies the normed values.  w holds C numbers or C / groups (wn says which).  VEC: four
+// consecutive coordinates per thread and access.
+template <typename Tin, typename Tg, bool VEC>
 __global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_stride, const Tg* __restrict__ gate, long gate_stride,
                                             const float* __restrict__ w, int wn, int rows, int C, int groups, float eps, int gate_first,
                                             Tg* __restrict__ out, long out_stride, float out_scale) {
+    __shared__ float part[8];
     const long unit = (long)blockIdx.x * blockDim.y + threadIdx.y;
-    if (unit >= (long)rows * groups) return;
-    const int row = (int)(unit / groups), g = (int)(unit - (long)row * groups), Cg = C / groups, lane = threadIdx.x;
+    const bool on = unit < (long)rows * groups;
+    const int row = on ? (int)(unit / groups) : 0, g = on ? (int)(unit - (long)row * groups) : 0, Cg = C / groups;
+    const int tx = threadIdx.x, TX = blockDim.x;
     const Tin* xr = x + (long)row * x_stride + (long)g * Cg;
     const Tg* gr = gate + (long)row * gate_stride + (long)g * Cg;
     float ss = 0.f;
-    for (int c = lane; c < Cg; c += 32) {
-        float v = ldf(xr + c);
-        if (gate_first) { const float z = ldf(gr + c); v *= z * sigmoidf_(z); }
-        ss = fmaf(v, v, ss);
+    if (on) {
+        if (VEC) {
+            for (int c = tx * 4; c < Cg; c += TX * 4) {
+                float4 v = ld4(xr + c);
+                if (gate_first) {
+                    const float4 z = ld4(gr + c);
+                    v.x *= z.x * sigmoidf_(z.x); v.y *= z.y * sigmoidf_(z.y); v.z *= z.z * sigmoidf_(z.z); v.w *= z.w * sigmoidf_(z.w);
+                }
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+        } else {
+            for (int c = tx; c < Cg; c += TX) {
+                float v = ldf(xr + c);
+                if (gate_first) { const float z = ldf(gr + c); v *= z * sigmoidf_(z); }
+                ss = fmaf(v, v, ss);
+            }
+        }
     }
-    const float inv = out_scale / sqrtf(warp_sum(ss) / (float)Cg + eps);
+    ss = warp_sum(ss);
+    if (TX > 32) {                              // one unit per block: fold the warps' sums
+        if ((tx & 31) == 0) part[tx >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int k = 0; k < TX / 32; ++k) ss += part[k];
+    }
+    if (!on) return;
+    const float inv = out_scale / sqrtf(ss / (float)Cg + eps);
     const float* wr = w + (wn == C ? (long)g * Cg : 0);
     Tg* o = out + (long)row * out_stride + (long)g * Cg;
-    for (int c = lane; c < Cg; c += 32) {
+    if (VEC) {
+        for (int c = tx * 4; c < Cg; c += TX * 4) {
+            const float4 v = ld4(xr + c), z = ld4(gr + c), u = ld4(wr + c);
+            st4(o + c, make_float4(v.x * (z.x * sigmoidf_(z.x)) * inv * u.x, v.y * (z.y * sigmoidf_(z.y)) * inv * u.y,
+                                   v.z * (z.z * sigmoidf_(z.z)) * inv * u.z, v.w * (z.w * sigmoidf_(z.w)) * inv * u.w));
+        }
+        return;
+    }
+    for (int c = tx; c < Cg; c += TX) {
         const float z = ldf(gr + c);
         stf(o + c, ldf(xr + c) * (z * sigmoidf_(z)) * inv * wr[c]);
     }
@@ -93,14 +126,21 @@ void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void*
                           cudaStream_t s) {
     const long units = (long)rows * groups;
     if (units == 0) return;
-    dim3 block(32, 8), grid((unsigned)((units + 7) / 8));
-#define SEQMIX_GN(TI, TG)                                                                                                             \
-    group_rms_norm_gated_kernel<TI, TG><<<grid, block, 0, s>>>((const TI*)x, x_stride, (const TG*)gate, gate_stride, w, wn, rows, C, groups, \
-                                                               eps, gate_first, (TG*)out, out_stride, out_scale)
+    const int Cg = C / groups;
+    const bool wide = Cg >= 1024;
+    dim3 block(wide ? 256 : 32, wide ? 1 : 8), grid((unsigned)(wide ? units : (units + 7) / 8));
+    const size_t ei = in_bf16 ? 2 : 4, eg = gate_bf16 ? 2 : 4;
+    const bool vec = Cg % 4 == 0 && x_stride % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && (uintptr_t)x % (4 * ei) == 0 &&
+                     (uintptr_t)gate % (4 * eg) == 0 && (uintptr_t)out % (4 * eg) == 0 && (uintptr_t)w % 16 == 0;
+#define SEQMIX_GN_V(TI, TG, V)                                                                                                        \
+    group_rms_norm_gated_kernel<TI, TG, V><<<grid, block, 0, s>>>((const TI*)x, x_stride, (const TG*)gate, gate_stride, w, wn, rows, C,  \
+                                                                  groups, eps, gate_first, (TG*)out, out_stride, out_scale)
+#define SEQMIX_GN(TI, TG) do { if (vec) SEQMIX_GN_V(TI, TG, true); else SEQMIX_GN_V(TI, TG, false); } while (0)
     if (in_bf16 && gate_bf16) SEQMIX_GN(bf16, bf16);
     else if (!in_bf16 && gate_bf16) SEQMIX_GN(float, bf16);
     else if (!in_bf16 && !gate_bf16) SEQMIX_GN(float, float);
     else SEQMIX_GN(bf16, float);
+#undef SEQMIX_GN_V
 #undef SEQMIX_GN
 }
 

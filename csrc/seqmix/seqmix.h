@@ -68,9 +68,17 @@ void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k
 bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
                              const void* gate, long g_sb, long g_st, int bf, const int* lens, int B, int S, int H, int G, int D, int V,
                              int window, float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s);
+bool window_prompt_mma_fits(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
+                            int D, int V, const void* out, long out_stride);
+void window_prompt_mma(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
+                       const void* gate, long g_sb, long g_st, const int* lens, int B, int S, int H, int G, int D, int V, int window,
+                       float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s);
+// part_m / part_l float [B, H, splits], part_acc float [B, H, splits, V] with splits = window_token_splits(...)
+int window_token_splits(int ring, int B, int H, int G);
 bool window_attention_token(const void* q, long q_sb, const void* kcache, const void* vcache, const void* gate, long g_sb, int bf,
                             const int* slots, const int* pos0, const int* lens, int ring, int B, int H, int G, int D, int V, int window,
-                            float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s);
+                            float scale, float softcap, int splits, float* part_m, float* part_l, float* part_acc, void* out,
+                            long out_stride, float out_scale, cudaStream_t s);
 // Matrix-state recurrences with one decay per head and token (matrix_recurrence.cu); false: the state has too many rows.
 bool gated_delta_scan(const void* q, const void* k, long qk_sb, long qk_st, const void* v, long v_sb, long v_st, int bf, const float* braw,
                       const float* araw, long ba_sb, long ba_st, const float* a_log, const float* dt_bias, float* state, const int* slots,

@@ -10,6 +10,12 @@ namespace seqmix {
 
 constexpr int kMaxTaps = 16;
 
+// silu of the convolution's result: the exact-rounded form for float outputs, fast exponential and division when the result is
+// rounded to bfloat16 anyway
+template <typename Tout> __device__ __forceinline__ float silu_out(float z);
+template <> __device__ __forceinline__ float silu_out<float>(float z) { return z * sigmoidf_(z); }
+template <> __device__ __forceinline__ float silu_out<bf16>(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+
 template <typename Tin, typename Tout>
 __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_st, const float* __restrict__ w,
                                   const float* __restrict__ bias, Tin* state, const int* __restrict__ slots,
@@ -40,7 +46,7 @@ __global__ void short_conv_kernel(const Tin* __restrict__ x, long x_sb, long x_s
                     }
                 }
                 if (residual) acc += ldf(xb + (long)t * x_st + c);
-                if (act) acc *= sigmoidf_(acc);
+                if (act) acc = silu_out<Tout>(acc);
             }
             stf(out + ((long)b * S + t) * C + c, acc);
         }
@@ -117,7 +123,7 @@ __global__ void short_conv_vec_kernel(const Tin* __restrict__ x, long x_sb, long
                     acc.x = fmaf(wl.x, cur.x, acc.x); acc.y = fmaf(wl.y, cur.y, acc.y);
                     acc.z = fmaf(wl.z, cur.z, acc.z); acc.w = fmaf(wl.w, cur.w, acc.w);
                     if (residual) { acc.x += cur.x; acc.y += cur.y; acc.z += cur.z; acc.w += cur.w; }
-                    if (act) { acc.x *= sigmoidf_(acc.x); acc.y *= sigmoidf_(acc.y); acc.z *= sigmoidf_(acc.z); acc.w *= sigmoidf_(acc.w); }
+                    if (act) { acc.x = silu_out<Tout>(acc.x); acc.y = silu_out<Tout>(acc.y); acc.z = silu_out<Tout>(acc.z); acc.w = silu_out<Tout>(acc.w); }
                 }
                 st4(out + ((long)b * S + t) * C + c, acc);
 #pragma unroll

@@ -7,10 +7,11 @@
 //   window_attention_prompt: prompts starting at position 0, keys and values of the call itself.  A block owns 16 consecutive
 //                            queries of one head (4 warps x 4 queries); key / value rows come through shared memory 32 at a time;
 //                            in the score pass a lane owns one key (4 queries per shared-memory read), in the value pass a lane
-//                            owns value columns lane, lane + 32, ...
-//   window_attention_token : one query per (sequence, head) against the ring.  A block owns one (sequence, head); its 4 warps take
-//                            ring chunks of 32 rows in turn (each through its own shared-memory buffer) and their partial softmaxes
-//                            are merged at the end.
+//                            owns value columns lane, lane + 32, ...  (float, and bfloat16 of sizes the fused tensor-core kernel
+//                            of window_prefill.cu does not take)
+//   window_attention_token : one query per (sequence, head) against the ring.  A block owns up to 4 query heads of one key/value
+//                            group (a warp each) over one stretch of ring rows, staged 32 rows at a time for all of them; a
+//                            second kernel folds the stretches' partial softmaxes.
 #include <math.h>
 
 #include "seq_common.cuh"
@@ -172,53 +173,81 @@ __global__ void __launch_bounds__(128) window_prompt_kernel(
     }
 }
 
-// shared per warp: Ks [kKeys][D+1], Vs [kKeys][V], Qs [D], Ps [kKeys]; then the merge area [kWarps][2 + 32*VPL]
-template <typename T, int VPL>
-__global__ void __launch_bounds__(128) window_token_kernel(
-    const T* __restrict__ q, long q_sb, const T* __restrict__ kcache, const T* __restrict__ vcache, const T* __restrict__ gate, long g_sb,
-    const int* __restrict__ slots, const int* __restrict__ pos0, const int* __restrict__ lens, int ring, int H, int G, int D, int V,
-    int window, float scale, float softcap, T* __restrict__ out, long out_stride, float out_scale) {
-    extern __shared__ float sm[];
-    const int DP = D + 1, per = kKeys * DP + kKeys * V + D + kKeys;
-    const int h = blockIdx.x, b = blockIdx.y, g = h / (H / G);
-    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
-    float* Ks = sm + wp * per;
-    float* Vs = Ks + kKeys * DP;
-    float* Qw = Vs + kKeys * V;
-    float* Pw = Qw + D;
-    float* mg = sm + kWarps * per;
-    T* o = out + (long)b * out_stride + (long)h * V;
-    if (lens[b] <= 0) {
-        for (int c = tid; c < V; c += 128) stf(o + c, 0.f);
-        return;
+// 16 bytes at a time when the row allows it (VEC), else element by element; rows at or past `valid` become zeros
+template <typename T, bool VEC>
+__device__ __forceinline__ void stage_rows(float* dst, int ld, const T* __restrict__ src, long row_stride, int valid, int cols, int tid,
+                                           int nthr) {
+    if (VEC) {
+        constexpr int E = 16 / sizeof(T);
+        const int per = cols / E;
+        for (int x = tid; x < kKeys * per; x += nthr) {
+            const int jj = x / per, c = (x - jj * per) * E;
+            float* d = dst + jj * ld + c;
+            if (jj < valid) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + (long)jj * row_stride + c);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int u = 0; u < E; ++u) d[u] = ldf(e + u);
+            } else {
+#pragma unroll
+                for (int u = 0; u < E; ++u) d[u] = 0.f;
+            }
+        }
+    } else {
+        for (int x = tid; x < kKeys * cols; x += nthr) {
+            const int jj = x / cols, c = x - jj * cols;
+            dst[jj * ld + c] = jj < valid ? ldf(src + (long)jj * row_stride + c) : 0.f;
+        }
     }
+}
+
+// Single tokens against their rings.  grid (ring splits, head quads, sequences): a block takes up to 4 query heads of one key/value
+// group (a warp each) over one stretch of ring rows, staged 32 rows at a time for all of them, and leaves a partial softmax per
+// head: part_m / part_l [B, H, splits], part_acc [B, H, splits, V].  shared: Ks [kKeys][D+1], Vs [kKeys][V], Qs [4][D], Ps [4][kKeys]
+template <typename T, int VPL, bool VEC>
+__global__ void __launch_bounds__(128) window_token_kernel(
+    const T* __restrict__ q, long q_sb, const T* __restrict__ kcache, const T* __restrict__ vcache, const int* __restrict__ slots,
+    const int* __restrict__ pos0, const int* __restrict__ lens, int ring, int H, int G, int D, int V, int window, float scale,
+    float softcap, int splits, float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc) {
+    extern __shared__ float sm[];
+    const int DP = D + 1;
+    float* Ks = sm;
+    float* Vs = Ks + kKeys * DP;
+    float* Qs = Vs + kKeys * V;
+    float* Ps = Qs + kWarps * D;
+    const int split = blockIdx.x, b = blockIdx.z, HG = H / G, qpg = (HG + kWarps - 1) / kWarps;
+    const int g = blockIdx.y / qpg, hq = (blockIdx.y - g * qpg) * kWarps;
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const bool has = hq + wp < HG;                                   // this warp has a head
+    const int h = g * HG + hq + wp;
     const int p = pos0[b];
-    for (int d = lane; d < D; d += 32) Qw[d] = ldf(q + (long)b * q_sb + (long)h * D + d);
-    __syncwarp();
+    const int rows = lens[b] > 0 ? min(ring, p + 1) : 0;             // ring rows that hold a position (rows 0..p before the ring wraps)
+    int per = (rows + splits - 1) / splits;
+    per = (per + kKeys - 1) / kKeys * kKeys;
+    const int r0 = split * per, r1 = min(rows, r0 + per);
+    float* Qw = Qs + wp * D;
+    float* Pw = Ps + wp * kKeys;
+    if (has)
+        for (int d = lane; d < D; d += 32) Qw[d] = ldf(q + (long)b * q_sb + (long)h * D + d);
     float m = -INFINITY, l = 0.f, acc[VPL];
 #pragma unroll
     for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
     const T* kb = kcache + (long)slots[b] * ring * G * D + (long)g * D;
     const T* vb = vcache + (long)slots[b] * ring * G * V + (long)g * V;
-    const int rows = min(ring, p + 1);                               // ring rows that hold a position (rows 0..p before the ring wraps)
-    for (int c0 = wp * kKeys; c0 < rows; c0 += kWarps * kKeys) {
-        for (int x = lane; x < kKeys * D; x += 32) {
-            const int jj = x / D, d = x - jj * D, rr = c0 + jj;
-            Ks[jj * DP + d] = rr < rows ? ldf(kb + (long)rr * G * D + d) : 0.f;
-        }
-        for (int x = lane; x < kKeys * V; x += 32) {
-            const int jj = x / V, d = x - jj * V, rr = c0 + jj;
-            Vs[x] = rr < rows ? ldf(vb + (long)rr * G * V + d) : 0.f;
-        }
-        __syncwarp();
+    for (int c0 = r0; c0 < r1; c0 += kKeys) {
+        __syncthreads();
+        stage_rows<T, VEC>(Ks, DP, kb + (long)c0 * G * D, (long)G * D, r1 - c0, D, tid, 128);
+        stage_rows<T, VEC>(Vs, V, vb + (long)c0 * G * V, (long)G * V, r1 - c0, V, tid, 128);
+        __syncthreads();
+        if (!has) continue;
         float s = 0.f;
         const float* kr = Ks + lane * DP;
         for (int d = 0; d < D; ++d) s = fmaf(Qw[d], kr[d], s);
         const int rr = c0 + lane;
         int back = (p - rr) % ring;                                  // how far back the position of ring row rr lies
         if (back < 0) back += ring;
-        const bool ok = rr < rows && back < window && p - back >= 0;
+        const bool ok = rr < r1 && back < window && p - back >= 0;
         const float sc = ok ? cap_score(s * scale, softcap, inv_cap) : -INFINITY;
         float mx = sc;
 #pragma unroll
@@ -242,32 +271,36 @@ __global__ void __launch_bounds__(128) window_token_kernel(
         }
         __syncwarp();
     }
+    if (!has) return;
     l = warp_sum(l);
-    float* mw = mg + wp * (2 + 32 * VPL);
-    if (lane == 0) { mw[0] = m; mw[1] = l; }
-#pragma unroll
-    for (int c = 0; c < VPL; ++c) mw[2 + c * 32 + lane] = acc[c];
-    __syncthreads();
-    if (wp != 0) return;
-    float mt = -INFINITY;
-    for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, mg[w * (2 + 32 * VPL)]);
-    float lt = 0.f;
-#pragma unroll
-    for (int c = 0; c < VPL; ++c) acc[c] = 0.f;
-    for (int w = 0; w < kWarps; ++w) {
-        const float* x = mg + w * (2 + 32 * VPL);
-        if (x[0] == -INFINITY) continue;
-        const float f = expf(x[0] - mt);
-        lt = fmaf(x[1], f, lt);
-#pragma unroll
-        for (int c = 0; c < VPL; ++c) acc[c] = fmaf(x[2 + c * 32 + lane], f, acc[c]);
-    }
-    float f = lt > 0.f ? out_scale / lt : 0.f;
-    if (gate) f *= sigmoidf_(ldf(gate + (long)b * g_sb + h));
+    const long o = ((long)b * H + h) * splits + split;
+    if (lane == 0) { part_m[o] = m; part_l[o] = l; }
 #pragma unroll
     for (int c = 0; c < VPL; ++c) {
         const int col = lane + 32 * c;
-        if (col < V) stf(o + col, acc[c] * f);
+        if (col < V) part_acc[o * V + col] = acc[c];
+    }
+}
+
+// grid (H, B): the splits' partial softmaxes of one (sequence, head) folded, gated, scaled and written
+template <typename T>
+__global__ void window_token_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                          const float* __restrict__ part_acc, const T* __restrict__ gate, long g_sb, int H, int V,
+                                          int splits, T* __restrict__ out, long out_stride, float out_scale) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const long o = ((long)b * H + h) * splits;
+    float mt = -INFINITY;
+    for (int s = 0; s < splits; ++s) mt = fmaxf(mt, part_m[o + s]);
+    float lt = 0.f;
+    for (int s = 0; s < splits; ++s)
+        if (part_m[o + s] > -INFINITY) lt = fmaf(part_l[o + s], expf(part_m[o + s] - mt), lt);
+    float f = lt > 0.f ? out_scale / lt : 0.f;
+    if (gate) f *= sigmoidf_(ldf(gate + (long)b * g_sb + h));
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < splits; ++s)
+            if (part_m[o + s] > -INFINITY) a = fmaf(part_acc[(o + s) * V + c], expf(part_m[o + s] - mt), a);
+        stf(out + (long)b * out_stride + (long)h * V + c, a * f);
     }
 }
 
@@ -298,6 +331,11 @@ bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k,
     const int vpl = value_cols_per_lane(V);
     if (!vpl) return false;
     if (B * S == 0) return true;
+    if (bf && window_prompt_mma_fits(q, q_sb, q_st, k, k_sb, k_st, v, v_sb, v_st, D, V, out, out_stride)) {
+        window_prompt_mma(q, q_sb, q_st, k, k_sb, k_st, v, v_sb, v_st, gate, g_sb, g_st, lens, B, S, H, G, D, V, window, scale, softcap, out,
+                          out_stride, out_scale, s);
+        return true;
+    }
     const size_t smem = sizeof(float) * ((size_t)kKeys * (D + 1) + (size_t)kKeys * V + (size_t)kWarps * D * kQW + kWarps * kKeys * kQW);
     dim3 grid((S + kWarps * kQW - 1) / (kWarps * kQW), H, B), block(128);
 #define SEQMIX_WP(T, P)                                                                                                               \
@@ -314,25 +352,40 @@ bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k,
     return true;
 }
 
+int window_token_splits(int ring, int B, int H, int G) {
+    const int quads = G * ((H / G + kWarps - 1) / kWarps);
+    const int want = (2 * 148 + B * quads - 1) / (B * quads);       // two blocks per SM's worth of work items
+    const int most = (ring + 4 * kKeys - 1) / (4 * kKeys);          // a split has at least 4 chunks
+    return max(1, min(min(want, most), 64));
+}
+
 bool window_attention_token(const void* q, long q_sb, const void* kcache, const void* vcache, const void* gate, long g_sb, int bf,
                             const int* slots, const int* pos0, const int* lens, int ring, int B, int H, int G, int D, int V, int window,
-                            float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s) {
+                            float scale, float softcap, int splits, float* part_m, float* part_l, float* part_acc, void* out,
+                            long out_stride, float out_scale, cudaStream_t s) {
     const int vpl = value_cols_per_lane(V);
     if (!vpl) return false;
     if (B == 0) return true;
-    const size_t smem = sizeof(float) * ((size_t)kWarps * (kKeys * (D + 1) + kKeys * V + D + kKeys) + kWarps * (2 + 32 * vpl));
-    dim3 grid(H, B), block(128);
-#define SEQMIX_WT(T, P)                                                                                                               \
+    const size_t smem = sizeof(float) * ((size_t)kKeys * (D + 1) + (size_t)kKeys * V + (size_t)kWarps * D + kWarps * kKeys);
+    const int quads = G * ((H / G + kWarps - 1) / kWarps), per16 = bf ? 8 : 4;
+    const bool vec = D % per16 == 0 && V % per16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0;
+    dim3 grid(splits, quads, B), block(128);
+#define SEQMIX_WT(T, P, VC)                                                                                                           \
     do {                                                                                                                              \
-        if (!raise_smem(window_token_kernel<T, P>, smem)) return false;                                                               \
-        window_token_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, q_sb, (const T*)kcache, (const T*)vcache, (const T*)gate, g_sb,  \
-                                                            slots, pos0, lens, ring, H, G, D, V, window, scale, softcap, (T*)out,      \
-                                                            out_stride, out_scale);                                                   \
+        if (!raise_smem(window_token_kernel<T, P, VC>, smem)) return false;                                                           \
+        window_token_kernel<T, P, VC><<<grid, block, smem, s>>>((const T*)q, q_sb, (const T*)kcache, (const T*)vcache, slots, pos0, lens, \
+                                                                ring, H, G, D, V, window, scale, softcap, splits, part_m, part_l,      \
+                                                                part_acc);                                                            \
     } while (0)
-#define SEQMIX_WT_T(P) do { if (bf) SEQMIX_WT(bf16, P); else SEQMIX_WT(float, P); } while (0)
+#define SEQMIX_WT_V(T, P) do { if (vec) SEQMIX_WT(T, P, true); else SEQMIX_WT(T, P, false); } while (0)
+#define SEQMIX_WT_T(P) do { if (bf) SEQMIX_WT_V(bf16, P); else SEQMIX_WT_V(float, P); } while (0)
     if (vpl == 2) SEQMIX_WT_T(2); else if (vpl == 4) SEQMIX_WT_T(4); else SEQMIX_WT_T(8);
 #undef SEQMIX_WT_T
+#undef SEQMIX_WT_V
 #undef SEQMIX_WT
+    dim3 mgrid(H, B);
+    if (bf) window_token_merge_kernel<bf16><<<mgrid, 128, 0, s>>>(part_m, part_l, part_acc, (const bf16*)gate, g_sb, H, V, splits, (bf16*)out, out_stride, out_scale);
+    else window_token_merge_kernel<float><<<mgrid, 128, 0, s>>>(part_m, part_l, part_acc, (const float*)gate, g_sb, H, V, splits, (float*)out, out_stride, out_scale);
     return true;
 }
 

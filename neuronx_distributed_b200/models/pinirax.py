@@ -147,8 +147,10 @@ def convert_state_dict(cfg: PiniraxConfig, sd: Dict[str, torch.Tensor]) -> Dict[
         if spec["type"] == "parallel":
             a, b = o + "mixer.branches.left.", o + "mixer.branches.right."
             H = int(m["left"]["heads"])
-            out[a + "in_proj"] = torch.cat([x("left.q"), x("left.k"), x("left.v"), x("left.g")], 0)
-            out[a + "in_bias"] = torch.cat([x("left.q.b"), x("left.k.b"), x("left.v.b"), torch.zeros(H, dtype=x("left.q.b").dtype)], 0)
+            stack = torch.cat([x("left.q"), x("left.k"), x("left.v"), x("left.g")], 0)
+            pad = GatedWindowAttention.stacked_rows(H, int(m["left"]["kv_heads"]), int(m["left"]["dim"]), int(m["left"]["vdim"])) - stack.shape[0]
+            out[a + "in_proj"] = torch.cat([stack, stack.new_zeros(pad, stack.shape[1])], 0)
+            out[a + "in_bias"] = torch.cat([x("left.q.b"), x("left.k.b"), x("left.v.b"), torch.zeros(H + pad, dtype=x("left.q.b").dtype)], 0)
             out[a + "q_norm"], out[a + "k_norm"], out[a + "o"] = x("left.q.norm"), x("left.k.norm"), x("left.o")
             out[b + "in_proj"] = torch.cat([x("right.q"), x("right.k"), x("right.v"), x("right.g")], 0)
             out[b + "ba_proj"] = torch.cat([x("right.b"), x("right.a")], 0)

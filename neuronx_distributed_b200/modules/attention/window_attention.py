@@ -30,10 +30,17 @@ class GatedWindowAttention(nn.Module):
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
         f32 = lambda *s: nn.Parameter(torch.ones(*s, dtype=torch.float32, device=device), requires_grad=False)
         self.n_q, self.n_k, self.n_v = heads * dim, kv_heads * dim, kv_heads * vdim
-        rows = self.n_q + self.n_k + self.n_v + (heads if head_gate else 0)
-        self.in_proj, self.in_bias = mk(rows, width), mk(rows)                       # rows: q | k | v | gate
+        rows = self.stacked_rows(heads, kv_heads, dim, vdim, head_gate)
+        self.in_proj, self.in_bias = mk(rows, width), mk(rows)                       # rows: q | k | v | gate | zero padding
         self.q_norm, self.k_norm = (f32(dim), f32(dim)) if qk_norm else (None, None)
         self.o = mk(width, heads * vdim)
+
+    @staticmethod
+    def stacked_rows(heads: int, kv_heads: int, dim: int, vdim: int, head_gate: bool = True) -> int:
+        """Rows of the stacked projection: q | k | v | gate, padded to a whole 8 so that token rows stay 16-byte aligned in bfloat16
+        (the fused prompt kernel reads q, k and v in place)."""
+        n = heads * dim + kv_heads * (dim + vdim) + (heads if head_gate else 0)
+        return -(-n // 8) * 8
 
     @property
     def out_features(self) -> int:
@@ -51,7 +58,7 @@ class GatedWindowAttention(nn.Module):
         p = F.linear(h, self.in_proj, self.in_bias)
         a, b, c = self.n_q, self.n_q + self.n_k, self.n_q + self.n_k + self.n_v
         q, k, v = p[..., :a].unflatten(-1, (H, D)), p[..., a:b].unflatten(-1, (G, D)), p[..., b:c].unflatten(-1, (G, V))
-        gate = p[..., c:] if self.head_gate else None
+        gate = p[..., c:c + H] if self.head_gate else None
         seqmix.window_qk_prepare(q, k, v, self.q_norm, self.k_norm, self.eps, ctx.pos0, ctx.lens, ctx.slots, st["k"], st["v"])
         if ctx.fresh:
             return seqmix.window_attention_prompt(q, k, v, gate, ctx.lens, self.window, self.scale, self.softcap, out, out_scale)

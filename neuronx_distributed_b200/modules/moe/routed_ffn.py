@@ -91,18 +91,25 @@ class RoutedFFN(nn.Module):
         from .blockwise import build_block_metadata
 
         e, bs = _ext.ext(), self.block_rows
-        b2e, tp2id, _ = build_block_metadata(idx, self.experts, bs)
-        b2e = b2e.to(torch.int32).contiguous()
+        ident = None
+        if self.identity_experts:                      # identity choices form one more group; its blocks run some expert's matrices
+            ident = idx >= self.experts                # (finite rows that the combine weighs with zero)
+            idx = torch.where(ident, torch.full_like(idx, self.experts), idx)
+        b2e, tp2id, _ = build_block_metadata(idx, self.experts + (1 if self.identity_experts else 0), bs)
+        group = b2e.long()                                                         # the group of every block, the extra one included
+        b2e = b2e.to(torch.int32).clamp(max=self.experts - 1).contiguous()
         tp = tp2id[: b2e.numel() * bs].long()
         x = h[tp.clamp(min=0)]
         _ext.count_launch(2)
         eo = e.grouped_gemm(self._act(e.grouped_gemm(x, self.up, b2e, bs, True)), self.down, b2e, bs, True)
         N, top = idx.shape                                                         # no host synchronisation: padding slots write
-        tok, exp = tp.clamp(min=0), b2e.long().repeat_interleave(bs)               # to a spare entry past the end
+        tok, exp = tp.clamp(min=0), group.repeat_interleave(bs)                    # to a spare entry past the end
         choice = (idx[tok] == exp[:, None]).to(torch.int32).argmax(1)
         flat = torch.empty(N * top + 1, dtype=torch.int32, device=h.device)
         flat[torch.where(tp >= 0, tok * top + choice, N * top)] = torch.arange(tp.numel(), dtype=torch.int32, device=h.device)
         src = flat[: N * top].view(N, top)
+        if ident is not None:
+            src = torch.where(ident, torch.zeros_like(src), src)                   # any row: its weight is zero
         return eo, src
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
@@ -120,7 +127,7 @@ class RoutedFFN(nn.Module):
             mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), "silu_glu" if self.gated else "gelu")
             eo = seqmix.indexed_gemv(self.down, sel, mid, None)
             src = torch.arange(M, device=h.device, dtype=torch.int32).view(N, self.top)
-        elif self._grouped_kernels(h) is not None and not self.identity_experts:
+        elif self._grouped_kernels(h) is not None:
             eo, src = self._experts_grouped(h, idx)
         else:
             flat = idx.reshape(-1)

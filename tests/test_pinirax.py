@@ -630,3 +630,31 @@ def test_bfloat16_routed_ffn_rows_with_a_clear_choice(rows):
     want = oracle.moe(h.double(), {k: v.double() for k, v in P.items()}, f)
     got = m(h.cuda()).cpu().double()
     assert ((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 32), (6, 2, 48, 96), (2, 1, 128, 128), (3, 3, 64, 16), (2, 2, 256, 256)])
+@pytest.mark.parametrize("window,softcap", [(1, 30.0), (7, 0.0), (64, 5.0), (100, 50.0), (1000, 20.0)])
+def test_bfloat16_prompt_attention_in_one_kernel(H, G, D, V, window, softcap):
+    """The fused tensor-core prompt kernel (bfloat16, sizes in whole 16s) against the float statement of the same op on the same
+    rounded inputs: unequal lengths, tiles cut by the window and by the end of a sequence, strided operands, gate and scale."""
+    g = torch.Generator().manual_seed(D + window)
+    B, S = 3, 200
+    lens = torch.tensor([200, 77, 1], dtype=torch.int32)
+    P = H * D + G * (D + V) + 8
+    p = (torch.randn(B, S, P, generator=g) * 1.5).to(torch.bfloat16)
+    q, k, v = p[..., :H * D].unflatten(-1, (H, D)), p[..., H * D:H * D + G * D].unflatten(-1, (G, D)), p[..., H * D + G * D:H * D + G * (D + V)].unflatten(-1, (G, V))
+    gate = p[..., -8:-8 + H]
+    scale = 2.0 / math.sqrt(D)
+    want = torch.zeros(B * S, H * V)
+    seqmix.window_attention_prompt(q.float(), k.float(), v.float(), gate.float(), lens, window, scale, softcap, want, 0.8)
+    pc = p.cuda()
+    qc, kc, vc = pc[..., :H * D].unflatten(-1, (H, D)), pc[..., H * D:H * D + G * D].unflatten(-1, (G, D)), pc[..., H * D + G * D:H * D + G * (D + V)].unflatten(-1, (G, V))
+    out = torch.full((B * S, H * V + 16), 7.0, dtype=torch.bfloat16, device="cuda")
+    seqmix.window_attention_prompt(qc, kc, vc, pc[..., -8:-8 + H], lens.cuda(), window, scale, softcap, out[:, 8:8 + H * V], 0.8)
+    got = out[:, 8:8 + H * V].float().cpu()
+    assert (out[:, :8] == 7).all() and (out[:, 8 + H * V:] == 7).all()
+    assert (got - want).abs().max() < 0.03 * max(1.0, want.abs().max().item())
+    assert ((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) < 1e-2
+    for b in range(B):
+        assert (got.view(B, S, -1)[b, lens[b]:] == 0).all()
