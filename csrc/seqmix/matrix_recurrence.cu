@@ -4,8 +4,9 @@
 //                      g = exp(-exp(a_log) softplus(araw + dt_bias)).  With A = M_old^T k and Bq = M_old^T q one pass over the old
 //                      state gives u = beta (v - g A) and o = g Bq + (k.q) u, and the update M = g M_old + k u^T follows in registers.
 //   ssd_scan         : dt = softplus(dtraw + dt_bias);  M <- exp(-exp(a_log) dt) M + dt b x^T;  y = M^T c + dskip x   (M [N, V])
-// A block owns 32 value columns of one (sequence, head): lane = column, warp = one of 8 row groups, a thread keeps rows
-// r, r + 8, ... of its column in registers, so state loads and stores are whole 128-byte rows.  Tokens are staged through shared
+// A block owns 32 value columns of one (sequence, head): lane = column, warp = one of 8 row groups, a thread keeps DPT consecutive
+// rows of its column in registers (rows past the state's size are zeros that never change), so state loads and stores are whole
+// 128-byte rows and a token's per-row numbers come from shared memory four at a time.  Tokens are staged through shared
 // memory 8 at a time (a warp prepares one token: norms, decays, gates, from numbers fetched one chunk ahead); the per-token sums over
 // rows are folded across the warps
 // through a double-buffered shared array (one barrier per token).  Tokens at or past lens[b] write zeros and leave the state alone.
@@ -23,9 +24,10 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
     const float* __restrict__ dt_bias, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int S,
     int H, int G, int D, int V, float qscale, float* __restrict__ out) {
     extern __shared__ float sm[];
-    float* sk = sm;                              // [kTok][D] unit keys
-    float* sq = sk + kTok * D;                   // [kTok][D] unit queries times qscale
-    float* sv = sq + kTok * D;                   // [kTok][kCols]
+    constexpr int Dp = DPT * kRowGroups;         // padded row count (>= D); rows past D hold zeros
+    float* sk = sm;                              // [kTok][Dp] unit keys
+    float* sq = sk + kTok * Dp;                  // [kTok][Dp] unit queries times qscale
+    float* sv = sq + kTok * Dp;                  // [kTok][kCols]
     float* sc = sv + kTok * kCols;               // [kTok][4]: g, beta, k.q
     float* part = sc + kTok * 4;                 // [2][2][kRowGroups][kCols]
     const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
@@ -36,9 +38,10 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
     float M[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r + i * kRowGroups;
+        const int d = r * DPT + i;
         M[i] = (!fresh && col && d < D) ? sp[(long)d * V + j] : 0.f;
     }
+    for (int x = threadIdx.x; x < 2 * kTok * Dp; x += 256) sm[x] = 0.f;       // the padding rows stay zero
     const float ea = expf(a_log[h]), db = dt_bias[h];
     // warp r prepares token t0 + r of every chunk; its raw numbers are fetched one chunk ahead, so that the loads fly during the
     // previous chunk's arithmetic
@@ -72,7 +75,7 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
 #pragma unroll
             for (int i = 0; i < DL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) { sq[r * D + d] = qraw[i] * iq; sk[r * D + d] = kraw[i] * ik; }
+                if (d < D) { sq[r * Dp + d] = qraw[i] * iq; sk[r * Dp + d] = kraw[i] * ik; }
             }
             sv[r * kCols + lane] = vraw;
             if (lane == 0) {
@@ -85,13 +88,21 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
         fetch(t0 + kTok + r);
         const int nt = min(kTok, len - t0);
         for (int u = 0; u < nt; ++u) {
-            const float* ku = sk + u * D;
-            const float* qu = sq + u * D;
+            const float* ku = sk + u * Dp + r * DPT;
+            const float* qu = sq + u * Dp + r * DPT;
+            float kr[DPT];
             float A = 0.f, Bq = 0.f;
+            if (DPT >= 4) {
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = r + i * kRowGroups;
-                if (d < D) { A = fmaf(M[i], ku[d], A); Bq = fmaf(M[i], qu[d], Bq); }
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ku + i), q4 = *reinterpret_cast<const float4*>(qu + i);
+                    kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
+                    A = fmaf(M[i], k4.x, fmaf(M[i + 1], k4.y, fmaf(M[i + 2], k4.z, fmaf(M[i + 3], k4.w, A))));
+                    Bq = fmaf(M[i], q4.x, fmaf(M[i + 1], q4.y, fmaf(M[i + 2], q4.z, fmaf(M[i + 3], q4.w, Bq))));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) { kr[i] = ku[i]; A = fmaf(M[i], kr[i], A); Bq = fmaf(M[i], qu[i], Bq); }
             }
             float* pb = part + ((t0 + u) & 1) * 2 * kRowGroups * kCols;
             pb[r * kCols + lane] = A;
@@ -104,17 +115,14 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
             const float uv = beta * (sv[u * kCols + lane] - g * A);
             if (r == 0 && col) out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(g, Bq, kq * uv);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = r + i * kRowGroups;
-                if (d < D) M[i] = fmaf(g, M[i], ku[d] * uv);
-            }
+            for (int i = 0; i < DPT; ++i) M[i] = fmaf(g, M[i], kr[i] * uv);
         }
     }
     if (col) {
         for (int t = len + r; t < S; t += kRowGroups) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
-            const int d = r + i * kRowGroups;
+            const int d = r * DPT + i;
             if (d < D && (len > 0 || fresh)) sp[(long)d * V + j] = M[i];
         }
     }
@@ -127,9 +135,10 @@ __global__ void __launch_bounds__(256) ssd_kernel(
     const float* __restrict__ dskip, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int S, int H,
     int G, int N, int V, float* __restrict__ out) {
     extern __shared__ float sm[];
-    float* sb = sm;                              // [kTok][N] dt * b
-    float* scm = sb + kTok * N;                  // [kTok][N] c
-    float* sx = scm + kTok * N;                  // [kTok][kCols]
+    constexpr int Np = DPT * kRowGroups;         // padded row count (>= N); rows past N hold zeros
+    float* sb = sm;                              // [kTok][Np] dt * b
+    float* scm = sb + kTok * Np;                 // [kTok][Np] c
+    float* sx = scm + kTok * Np;                 // [kTok][kCols]
     float* sc = sx + kTok * kCols;               // [kTok][2]: decay
     float* part = sc + kTok * 2;                 // [2][kRowGroups][kCols]
     const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
@@ -140,9 +149,10 @@ __global__ void __launch_bounds__(256) ssd_kernel(
     float M[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = r + i * kRowGroups;
+        const int d = r * DPT + i;
         M[i] = (!fresh && col && d < N) ? sp[(long)d * V + j] : 0.f;
     }
+    for (int x = threadIdx.x; x < 2 * kTok * Np; x += 256) sm[x] = 0.f;       // the padding rows stay zero
     const float ea = expf(a_log[h]), db = dt_bias[h], ds = dskip[h];
     constexpr int DL = DPT >= 4 ? DPT / 4 : 1;   // state rows per lane when a warp prepares a token: N <= 8 DPT = 32 DL
     float braw[DL], craw[DL], xraw = 0.f, dtr = 0.f;
@@ -168,7 +178,7 @@ __global__ void __launch_bounds__(256) ssd_kernel(
 #pragma unroll
             for (int i = 0; i < DL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < N) { sb[r * N + d] = dt * braw[i]; scm[r * N + d] = craw[i]; }
+                if (d < N) { sb[r * Np + d] = dt * braw[i]; scm[r * Np + d] = craw[i]; }
             }
             sx[r * kCols + lane] = xraw;
             if (lane == 0) sc[r * 2] = expf(-ea * dt);
@@ -177,14 +187,21 @@ __global__ void __launch_bounds__(256) ssd_kernel(
         fetch(t0 + kTok + r);
         const int nt = min(kTok, len - t0);
         for (int u = 0; u < nt; ++u) {
-            const float* bu = sb + u * N;
-            const float* cu = scm + u * N;
+            const float* bu = sb + u * Np + r * DPT;
+            const float* cu = scm + u * Np + r * DPT;
             const float dec = sc[u * 2], xv = sx[u * kCols + lane];
             float y = 0.f;
+            if (DPT >= 4) {
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = r + i * kRowGroups;
-                if (d < N) { M[i] = fmaf(dec, M[i], bu[d] * xv); y = fmaf(M[i], cu[d], y); }
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bu + i), c4 = *reinterpret_cast<const float4*>(cu + i);
+                    M[i] = fmaf(dec, M[i], b4.x * xv); M[i + 1] = fmaf(dec, M[i + 1], b4.y * xv);
+                    M[i + 2] = fmaf(dec, M[i + 2], b4.z * xv); M[i + 3] = fmaf(dec, M[i + 3], b4.w * xv);
+                    y = fmaf(M[i], c4.x, fmaf(M[i + 1], c4.y, fmaf(M[i + 2], c4.z, fmaf(M[i + 3], c4.w, y))));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) { M[i] = fmaf(dec, M[i], bu[i] * xv); y = fmaf(M[i], cu[i], y); }
             }
             float* pb = part + ((t0 + u) & 1) * kRowGroups * kCols;
             pb[r * kCols + lane] = y;
@@ -201,7 +218,7 @@ __global__ void __launch_bounds__(256) ssd_kernel(
         for (int t = len + r; t < S; t += kRowGroups) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
-            const int d = r + i * kRowGroups;
+            const int d = r * DPT + i;
             if (d < N && (len > 0 || fresh)) sp[(long)d * V + j] = M[i];
         }
     }
@@ -221,7 +238,7 @@ bool gated_delta_scan(const void* q, const void* k, long qk_sb, long qk_st, cons
     if (!dpt) return false;
     if (B == 0 || S == 0) return true;
     dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
-    const size_t smem = sizeof(float) * (2 * kTok * D + kTok * kCols + kTok * 4 + 2 * 2 * kRowGroups * kCols);
+    const size_t smem = sizeof(float) * (2 * kTok * dpt * kRowGroups + kTok * kCols + kTok * 4 + 2 * 2 * kRowGroups * kCols);
 #define SEQMIX_GDR(T, P)                                                                                                              \
     gated_delta_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, (const T*)k, qk_sb, qk_st, (const T*)v, v_sb, v_st, braw, araw, ba_sb, \
                                                        ba_st, a_log, dt_bias, state, slots, lens, fresh, S, H, G, D, V, qscale, out)
@@ -247,7 +264,7 @@ bool ssd_scan(const void* x, long x_sb, long x_st, const void* bm, const void* c
     if (!dpt) return false;
     if (B == 0 || S == 0) return true;
     dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
-    const size_t smem = sizeof(float) * (2 * kTok * N + kTok * kCols + kTok * 2 + 2 * kRowGroups * kCols);
+    const size_t smem = sizeof(float) * (2 * kTok * dpt * kRowGroups + kTok * kCols + kTok * 2 + 2 * kRowGroups * kCols);
 #define SEQMIX_SSD(T, P)                                                                                                              \
     ssd_kernel<T, P><<<grid, block, smem, s>>>((const T*)x, x_sb, x_st, (const T*)bm, (const T*)cm, bc_sb, bc_st, dtraw, dt_sb, dt_st,   \
                                                a_log, dt_bias, dskip, state, slots, lens, fresh, S, H, G, N, V, out)
