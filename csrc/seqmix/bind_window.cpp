@@ -45,7 +45,7 @@ void window_attention_prompt(const Tensor& q, const Tensor& k, const Tensor& v, 
     bool ok = seqmix::window_attention_prompt(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(),
                                               v.stride(0), v.stride(1), gp, g_sb, g_st, is_bf(q), i32(lens), B, S, H, G, D, V, (int)window,
                                               (float)scale, (float)softcap, out.data_ptr(), out.stride(0), (float)out_scale, stream());
-    TORCH_CHECK(ok, "window_attention_prompt: sizes do not fit the kernel (vdim <= 256)");
+    TORCH_CHECK(ok, "window_attention_prompt: sizes do not fit the kernel (vdim <= 512)");
     check_launch();
 }
 
@@ -71,7 +71,7 @@ void window_attention_token(const Tensor& q, const Tensor& kcache, const Tensor&
                                              i32(pos0), i32(lens), ring, B, H, G, D, V, (int)window, (float)scale, (float)softcap, splits,
                                              pm.data_ptr<float>(), pl.data_ptr<float>(), pa.data_ptr<float>(), out.data_ptr(),
                                              out.stride(0), (float)out_scale, stream());
-    TORCH_CHECK(ok, "window_attention_token: sizes do not fit the kernel (vdim <= 256)");
+    TORCH_CHECK(ok, "window_attention_token: sizes do not fit the kernel (vdim <= 512)");
     check_launch();
 }
 

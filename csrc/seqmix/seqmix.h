@@ -61,7 +61,7 @@ void embed_sinusoid(const long* tokens, const void* table, int bf, float scale, 
 void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,
                           int wn, int rows, int C, int groups, float eps, int gate_first, void* out, long out_stride, float out_scale,
                           cudaStream_t s);
-// Grouped-query sliding-window attention (window_attention.cu); false: sizes do not fit (value size above 256).
+// Grouped-query sliding-window attention (window_attention.cu); false: sizes do not fit (value size above 512).
 void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st, int bf,
                        const float* qw, const float* kw, float eps, const int* pos0, const int* lens, const int* slots, void* kcache,
                        void* vcache, int ring, int B, int S, int H, int G, int D, int V, cudaStream_t s);

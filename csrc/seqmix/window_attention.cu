@@ -317,7 +317,7 @@ void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k
                                                               eps, pos0, lens, slots, (float*)kcache, (float*)vcache, ring, S, H, G, D, V);
 }
 
-static int value_cols_per_lane(int V) { return V <= 64 ? 2 : (V <= 128 ? 4 : (V <= 256 ? 8 : 0)); }
+static int value_cols_per_lane(int V) { return V <= 64 ? 2 : (V <= 128 ? 4 : (V <= 256 ? 8 : (V <= 512 ? 16 : 0))); }
 
 template <typename K>
 static bool raise_smem(K kernel, size_t smem) {
@@ -346,7 +346,7 @@ bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k,
                                                              (T*)out, out_stride, out_scale);                                         \
     } while (0)
 #define SEQMIX_WP_T(P) do { if (bf) SEQMIX_WP(bf16, P); else SEQMIX_WP(float, P); } while (0)
-    if (vpl == 2) SEQMIX_WP_T(2); else if (vpl == 4) SEQMIX_WP_T(4); else SEQMIX_WP_T(8);
+    if (vpl == 2) SEQMIX_WP_T(2); else if (vpl == 4) SEQMIX_WP_T(4); else if (vpl == 8) SEQMIX_WP_T(8); else SEQMIX_WP_T(16);
 #undef SEQMIX_WP_T
 #undef SEQMIX_WP
     return true;
@@ -379,7 +379,7 @@ bool window_attention_token(const void* q, long q_sb, const void* kcache, const 
     } while (0)
 #define SEQMIX_WT_V(T, P) do { if (vec) SEQMIX_WT(T, P, true); else SEQMIX_WT(T, P, false); } while (0)
 #define SEQMIX_WT_T(P) do { if (bf) SEQMIX_WT_V(bf16, P); else SEQMIX_WT_V(float, P); } while (0)
-    if (vpl == 2) SEQMIX_WT_T(2); else if (vpl == 4) SEQMIX_WT_T(4); else SEQMIX_WT_T(8);
+    if (vpl == 2) SEQMIX_WT_T(2); else if (vpl == 4) SEQMIX_WT_T(4); else if (vpl == 8) SEQMIX_WT_T(8); else SEQMIX_WT_T(16);
 #undef SEQMIX_WT_T
 #undef SEQMIX_WT_V
 #undef SEQMIX_WT

@@ -227,7 +227,7 @@ def test_routed_ffn_choice_bias_and_identity_experts(device, rows, experts, iden
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("H,G,D,V,window,softcap", [(4, 2, 24, 40, 7, 20.0), (3, 3, 48, 96, 33, 0.0), (6, 1, 8, 130, 1, 5.0), (2, 2, 72, 16, 64, 30.0)])
+@pytest.mark.parametrize("H,G,D,V,window,softcap", [(4, 2, 24, 40, 7, 20.0), (3, 3, 48, 96, 33, 0.0), (6, 1, 8, 130, 1, 5.0), (2, 2, 72, 16, 64, 30.0), (2, 1, 40, 300, 9, 10.0)])
 def test_window_attention_prompt_and_ring(device, H, G, D, V, window, softcap):
     """The attention ops alone: a batch of prompts of unequal lengths, then single tokens against the rings, with a gate and scale."""
     g = torch.Generator().manual_seed(H * D)
