@@ -7,6 +7,8 @@
 //                  1: gelu_erf, 2: the matrix stacks gate rows over up rows and out = silu(gate row . x) * (up row . x), O/2 columns;
 //                  rows whose sel names no matrix give zeros
 //   moe_combine  : y[n,:] = base_weight[n] * base[n,:] + sum_k weight[n,k] * rows[src[n,k],:], summed in float
+//   route_topk   : scores, choice with a correction, top-k, weights and the identity experts' share in one launch
+//   small_linear_f32 : a few rows times a matrix with float results (router logits, per-head scalars of the recurrences)
 #include "seq_common.cuh"
 #include "seqmix.h"
 
@@ -106,6 +108,106 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
     float acc = base ? ldf(base + (long)n * C + c) * (base_weight ? base_weight[n] : 1.f) : 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(weight[(long)n * top + k], ldf(rows + (long)src[(long)n * top + k] * C + c), acc);
     stf(out + (long)n * C + c, acc);
+}
+
+// Router: a warp per row.  scores = softmax (kind 1) or sigmoid (kind 0) of the row's logits; the `top` largest of scores + correction
+// are chosen (ties: the lower index), in descending order; a chosen real expert (index < n_real) gets weight score * scale, a chosen
+// identity expert weight 0 while its score is added to ident[row].  PL: logits per lane (E <= 32 PL).
+template <int PL>
+__global__ void route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int N, int E, int top, int n_real,
+                                  int kind, float scale, float* __restrict__ w, long* __restrict__ idx, float* __restrict__ ident) {
+    const int row = blockIdx.x * blockDim.y + threadIdx.y, lane = threadIdx.x;
+    if (row >= N) return;
+    const float* z = logits + (long)row * E;
+    float sc[PL], ch[PL];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PL; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = e < E ? z[e] : -INFINITY;
+        mx = fmaxf(mx, sc[i]);
+    }
+    if (kind == 1) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < PL; ++i) { sc[i] = lane + 32 * i < E ? expf(sc[i] - mx) : 0.f; sum += sc[i]; }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int i = 0; i < PL; ++i) sc[i] = sc[i] / sum;
+    } else {
+#pragma unroll
+        for (int i = 0; i < PL; ++i) sc[i] = lane + 32 * i < E ? sigmoidf_(sc[i]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < PL; ++i) {
+        const int e = lane + 32 * i;
+        ch[i] = e < E ? sc[i] + (correction ? correction[e] : 0.f) : -INFINITY;
+    }
+    float idw = 0.f;
+    for (int t = 0; t < top; ++t) {
+        float bv = -INFINITY, bs = 0.f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < PL; ++i)
+            if (ch[i] > bv) { bv = ch[i]; bs = sc[i]; be = lane + 32 * i; }      // ascending e within a lane: ties keep the lower index
+        float v = bv;
+        int e = be;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, e, o);
+            if (ov > v || (ov == v && oe < e)) { v = ov; e = oe; }
+        }
+        const float s_e = __shfl_sync(0xffffffffu, bs, e & 31);                  // the owner's best is the winner
+        if ((e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < PL; ++i)
+                if (lane + 32 * i == e) ch[i] = -INFINITY;
+        }
+        if (lane == 0) {
+            idx[(long)row * top + t] = e;
+            w[(long)row * top + t] = e < n_real ? s_e * scale : 0.f;
+            if (e >= n_real) idw += s_e;
+        }
+    }
+    if (lane == 0 && ident) ident[row] = idw;
+}
+
+bool route_topk(const float* logits, const float* correction, int N, int E, int top, int n_real, int kind, float scale, float* w, long* idx,
+                float* ident, cudaStream_t s) {
+    if (E > 256 || top > E) return false;
+    if (N == 0) return true;
+    dim3 block(32, 4), grid((N + 3) / 4);
+    const int pl = (E + 31) / 32;
+#define SEQMIX_ROUTE(P) route_topk_kernel<P><<<grid, block, 0, s>>>(logits, correction, N, E, top, n_real, kind, scale, w, idx, ident)
+    if (pl <= 1) SEQMIX_ROUTE(1); else if (pl <= 2) SEQMIX_ROUTE(2); else if (pl <= 4) SEQMIX_ROUTE(4); else SEQMIX_ROUTE(8);
+#undef SEQMIX_ROUTE
+    return true;
+}
+
+// out[n, o] = w[o, :] . x[n, :] in float for a few rows n (a warp per output; w float or bfloat16, x float or bfloat16)
+template <typename Tw, typename Tx>
+__global__ void small_linear_f32_kernel(const Tw* __restrict__ w, const Tx* __restrict__ x, long x_stride, int N, int O, int I,
+                                        float* __restrict__ out) {
+    const int o = blockIdx.x * blockDim.y + threadIdx.y, n = blockIdx.y, lane = threadIdx.x;
+    if (o >= O) return;
+    const Tw* wr = w + (long)o * I;
+    const Tx* xr = x + (long)n * x_stride;
+    float acc = 0.f;
+    for (int i = lane; i < I; i += 32) acc = fmaf(ldf(wr + i), ldf(xr + i), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[(long)n * O + o] = acc;
+}
+
+void small_linear_f32(const void* w, int w_bf, const void* x, int x_bf, long x_stride, int N, int O, int I, float* out, cudaStream_t s) {
+    if (N * O == 0) return;
+    dim3 block(32, 8), grid((O + 7) / 8, N);
+    if (w_bf && x_bf) small_linear_f32_kernel<bf16, bf16><<<grid, block, 0, s>>>((const bf16*)w, (const bf16*)x, x_stride, N, O, I, out);
+    else if (!w_bf && x_bf) small_linear_f32_kernel<float, bf16><<<grid, block, 0, s>>>((const float*)w, (const bf16*)x, x_stride, N, O, I, out);
+    else if (w_bf && !x_bf) small_linear_f32_kernel<bf16, float><<<grid, block, 0, s>>>((const bf16*)w, (const float*)x, x_stride, N, O, I, out);
+    else small_linear_f32_kernel<float, float><<<grid, block, 0, s>>>((const float*)w, (const float*)x, x_stride, N, O, I, out);
 }
 
 void xielu(const void* x, void* out, int bf, long n, float ap, float an, cudaStream_t s) {

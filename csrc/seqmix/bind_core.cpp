@@ -125,7 +125,34 @@ void group_rms_norm_gated(const Tensor& x, const Tensor& gate, const Tensor& w, 
     check_launch();
 }
 
+// logits float [N,E] → (weights float [N,top], expert ids int64 [N,top], identity share float [N]); kind 1: softmax, 0: sigmoid
+std::vector<Tensor> route_topk(const Tensor& logits, const c10::optional<Tensor>& correction, int64_t top, int64_t n_real, int64_t kind,
+                               double scale) {
+    TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kFloat, "logits must be float [N,E]");
+    const int N = logits.size(0), E = logits.size(1);
+    TORCH_CHECK(!correction || correction->numel() == E, "the correction holds one number per expert");
+    Tensor w = at::empty({N, top}, logits.options()), idx = at::empty({N, top}, logits.options().dtype(at::kLong));
+    Tensor ident = at::empty({N}, logits.options());
+    bool ok = seqmix::route_topk(logits.data_ptr<float>(), correction ? f32(*correction) : nullptr, N, E, (int)top, (int)n_real, (int)kind,
+                                 (float)scale, w.data_ptr<float>(), idx.data_ptr<int64_t>(), ident.data_ptr<float>(), stream());
+    TORCH_CHECK(ok, "route_topk: at most 256 experts and top <= experts");
+    check_launch();
+    return {w, idx, ident};
+}
+
+// x [N, I] (row stride free), w [O, I] contiguous → float [N, O]
+Tensor small_linear_f32(const Tensor& x, const Tensor& w) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && w.dim() == 2 && w.is_contiguous() && w.size(1) == x.size(1), "bad operands");
+    Tensor out = at::empty({x.size(0), w.size(0)}, x.options().dtype(at::kFloat));
+    seqmix::small_linear_f32(w.data_ptr(), is_bf(w), x.data_ptr(), is_bf(x), x.stride(0), (int)x.size(0), (int)w.size(0), (int)x.size(1),
+                             out.data_ptr<float>(), stream());
+    check_launch();
+    return out;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("route_topk", &route_topk);
+    m.def("small_linear_f32", &small_linear_f32);
     m.def("short_conv", &short_conv);
     m.def("rms_norm", &rms_norm);
     m.def("add_rms_norm_", &add_rms_norm_);

@@ -56,6 +56,10 @@ void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_s
                   cudaStream_t s);
 void moe_combine(const void* rows, const int* src, const float* weight, const void* base, const float* base_weight, int bf, int N, int top,
                  int C, void* out, cudaStream_t s);
+// false: more experts than the kernel takes (256)
+bool route_topk(const float* logits, const float* correction, int N, int E, int top, int n_real, int kind, float scale, float* w, long* idx,
+                float* ident, cudaStream_t s);
+void small_linear_f32(const void* w, int w_bf, const void* x, int x_bf, long x_stride, int N, int O, int I, float* out, cudaStream_t s);
 void embed_sinusoid(const long* tokens, const void* table, int bf, float scale, const float* inv_freq, const int* pos0, int B, int S, int W,
                     int vocab, float* out, cudaStream_t s);
 void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,

@@ -50,6 +50,8 @@ class RoutedFFN(nn.Module):
         exactly — a checkpoint stored in bfloat16 — the product runs on the bfloat16 operands with float accumulation: the same
         products and a float sum, on the tensor cores.  Otherwise the framework router's float product."""
         w = self.router.linear_router.weight
+        if h.is_cuda and h.shape[0] <= seqmix.SMALL_LINEAR_ROWS and self.router.linear_router.bias is None:
+            return seqmix.linear_f32(h, w)                         # a warp per (row, expert): float products of the stored numbers
         if h.dtype != torch.bfloat16 or not h.is_cuda or self.router.linear_router.bias is not None:
             return self.router.get_router_logits(h)
         if self._router_lowp is None or self._router_lowp[0] != w._version:
@@ -60,14 +62,11 @@ class RoutedFFN(nn.Module):
         return seqmix.matmul_f32(h[None], self._router_lowp[1][None])[0]
 
     def route(self, h: torch.Tensor):
-        """Float scores of all experts → (weights ``[N, top]`` float, expert ids ``[N, top]``)."""
-        scores = self.router.apply_activation_fn(self._router_logits(h))
-        if self.correction is None:
-            w, idx = torch.topk(scores, self.top, dim=-1)
-        else:
-            idx = torch.topk(scores + self.correction, self.top, dim=-1).indices
-            w = scores.gather(1, idx)
-        return (w * self.weight_scale if self.weight_scale != 1.0 else w), idx
+        """Float scores of all experts → (weights ``[N, top]`` float, expert ids ``[N, top]``, identity share ``[N]`` float or None):
+        one kernel for scores, correction, top-k and the identity experts' share (``seqmix.route_topk``)."""
+        w, idx, ident = seqmix.route_topk(self._router_logits(h), self.correction, self.top, self.experts, self.router.act_fn,
+                                          self.weight_scale)
+        return w, idx, (ident if self.identity_experts else None)
 
     def _act(self, y: torch.Tensor) -> torch.Tensor:
         """The experts' activation on the up-projection's output: ``[M, ff]`` (plain) or ``[M, 2 ff]`` → ``[M, ff]`` (gated)."""
@@ -115,13 +114,8 @@ class RoutedFFN(nn.Module):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """``h [N, width]`` → ``[N, width]``."""
         N = h.shape[0]
-        w, idx = self.route(h)
+        w, idx, ident_w = self.route(h)                            # identity choices: weight 0, their scores summed in ident_w
         M = N * self.top
-        ident_w = None
-        if self.identity_experts:                                  # identity choices: weight moved to the input's own term
-            ident = idx >= self.experts
-            ident_w = torch.where(ident, w, torch.zeros_like(w)).sum(1)
-            w = torch.where(ident, torch.zeros_like(w), w)
         if M <= self.small_batch_rows:
             sel = idx.reshape(-1).to(torch.int32)                  # the streaming kernels skip rows that name no matrix
             mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), "silu_glu" if self.gated else "gelu")

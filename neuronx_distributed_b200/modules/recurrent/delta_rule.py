@@ -51,7 +51,7 @@ class GatedDeltaRule(nn.Module):
         c = self.conv(p[..., :nc], st["conv"], ctx, h.dtype, silu=True)              # [B,S,q|k|v]
         q, k = c[..., :self.n_qk].unflatten(-1, (G, D)), c[..., self.n_qk:2 * self.n_qk].unflatten(-1, (G, D))
         v = c[..., 2 * self.n_qk:].unflatten(-1, (H, V))
-        ba = seqmix.matmul_f32(h.view(1, N, W), self.ba_proj.t()[None]).view(B, S, 2 * H)
+        ba = seqmix.linear_f32(h.view(N, W), self.ba_proj).view(B, S, 2 * H)
         o = seqmix.gated_delta_scan(q, k, v, ba[..., :H], ba[..., H:], self.a_log, self.dt_bias, st["rec"], ctx.slots, ctx.lens, ctx.fresh)
         return seqmix.group_rms_norm_gated(o.view(N, H * V), p.view(N, -1)[:, nc:], self.norm, H, self.eps, False, out, out_scale)
 

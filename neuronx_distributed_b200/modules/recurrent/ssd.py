@@ -50,7 +50,7 @@ class SelectiveStateSpace(nn.Module):
         c = self.conv(p[..., I:], st["conv"], ctx, h.dtype, silu=True)               # [B,S,x|B|C]
         x = c[..., :I].unflatten(-1, (H, V))
         bm, cm = c[..., I:I + G * Ns].unflatten(-1, (G, Ns)), c[..., I + G * Ns:].unflatten(-1, (G, Ns))
-        dt = seqmix.matmul_f32(h.view(1, N, W), self.dt_proj.t()[None]).view(B, S, H)
+        dt = seqmix.linear_f32(h.view(N, W), self.dt_proj).view(B, S, H)
         y = seqmix.ssd_scan(x, bm, cm, dt, self.a_log, self.dt_bias, self.d_skip, st["rec"], ctx.slots, ctx.lens, ctx.fresh)
         return seqmix.group_rms_norm_gated(y.view(N, I), p.view(N, -1)[:, :I], self.norm, self.norm_groups, self.eps, True, out, out_scale)
 

@@ -30,7 +30,7 @@ CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
 GROUPS = {
     "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "bind_core.cpp"],
              ["short_conv", "rms_norm", "add_rms_norm_", "xielu", "gelu_erf", "silu_mul", "indexed_gemv", "moe_combine", "embed_sinusoid",
-              "group_rms_norm_gated"]),
+              "group_rms_norm_gated", "route_topk", "small_linear_f32"]),
     "latent": (["latent_attention.cu", "latent_decode.cu", "latent_prefill.cu", "bind_latent.cpp"],
                ["latent_kv_store", "rope_q_", "latent_window_attention", "window_softmax", "latent_prompt_attention",
                 "latent_prompt_attention_fits"]),
@@ -284,6 +284,40 @@ def window_softmax(scores: torch.Tensor, scale: float, ring_mode: bool, H: int, 
         ok = ok[:, :, :, None, :].expand(-1, -1, -1, H, -1).reshape(scores.shape)
     sc = (scores.float() * scale).masked_fill(~ok.expand(scores.shape), float("-inf"))
     return torch.nan_to_num(torch.softmax(sc, -1), nan=0.0).to(out_dtype)
+
+
+SMALL_LINEAR_ROWS = 16        # up to this many rows a float-result product runs as one warp per output
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x [N, I]`` (row stride free) times ``w [O, I]`` → float ``[N, O]``: the operands as they are stored, float accumulation and
+    a float result (router logits; per-head scalars that enter a recurrence)."""
+    if _cuda(x) and x.shape[0] <= SMALL_LINEAR_ROWS and x.stride(-1) == 1:
+        _ext.count_launch()
+        return ext().small_linear_f32(x, w)
+    if x.dtype == torch.float32 or not x.is_cuda:
+        return F.linear(x.float(), w.float())
+    return torch.bmm(x[None], w.to(x.dtype).t()[None], out_dtype=torch.float32)[0]
+
+
+ROUTE_MAX_EXPERTS = 256
+
+
+def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_real: int, act: str = "softmax", scale: float = 1.0):
+    """Float router logits ``[N, E]`` → ``(weights [N, top] float, expert ids [N, top] int64, identity share [N] float)``.
+    ``scores = softmax / sigmoid(logits)``; the ``top`` largest of ``scores + correction`` are chosen (descending); a chosen expert
+    below ``n_real`` gets weight ``score * scale``, a chosen expert from ``n_real`` on (an identity expert) gets weight 0 and adds its
+    score to the row's identity share."""
+    if _cuda(logits) and logits.shape[1] <= ROUTE_MAX_EXPERTS:
+        _ext.count_launch()
+        w, idx, ident = ext().route_topk(logits.contiguous(), correction, top, n_real, 1 if act == "softmax" else 0, float(scale))
+        return w, idx, ident
+    scores = torch.softmax(logits.float(), -1) if act == "softmax" else torch.sigmoid(logits.float())
+    idx = torch.topk(scores if correction is None else scores + correction, top, dim=-1).indices
+    w = scores.gather(1, idx)
+    real = idx < n_real
+    ident = torch.where(real, torch.zeros_like(w), w).sum(1)
+    return torch.where(real, w * scale, torch.zeros_like(w)), idx, ident
 
 
 def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
