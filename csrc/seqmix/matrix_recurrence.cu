@@ -9,7 +9,8 @@
 // 128-byte rows and a token's per-row numbers come from shared memory four at a time.  Tokens are staged through shared
 // memory 8 at a time (a warp prepares one token: norms, decays, gates, from numbers fetched one chunk ahead); the per-token sums over
 // rows are folded across the warps
-// through a double-buffered shared array (one barrier per token).  Tokens at or past lens[b] write zeros and leave the state alone.
+// through a shared array: one barrier per token in the delta rule (its write needs the sum), one per 8 tokens in the state space scan
+// (its read-out does not feed back).  Tokens at or past lens[b] write zeros and leave the state alone.
 #include "seq_common.cuh"
 #include "seqmix.h"
 
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256) ssd_kernel(
     float* scm = sb + kTok * Np;                 // [kTok][Np] c
     float* sx = scm + kTok * Np;                 // [kTok][kCols]
     float* sc = sx + kTok * kCols;               // [kTok][2]: decay
-    float* part = sc + kTok * 2;                 // [2][kRowGroups][kCols]
+    float* part = sc + kTok * 2;                 // [kTok][kRowGroups][kCols]
     const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
     const int lane = threadIdx.x & 31, r = threadIdx.x >> 5, j = j0 + lane;
     const int len = min(lens[b], S), hg = h / (H / G);
@@ -185,33 +186,41 @@ __global__ void __launch_bounds__(256) ssd_kernel(
         }
         __syncthreads();
         fetch(t0 + kTok + r);
+        // the read-out does not feed back into the state: the chunk's tokens run without a barrier between them, their row sums
+        // meet afterwards (warp r folds and writes token t0 + r)
         const int nt = min(kTok, len - t0);
-        for (int u = 0; u < nt; ++u) {
-            const float* bu = sb + u * Np + r * DPT;
-            const float* cu = scm + u * Np + r * DPT;
-            const float dec = sc[u * 2], xv = sx[u * kCols + lane];
-            float y = 0.f;
-            if (DPT >= 4) {
+        float yp[kTok];
 #pragma unroll
-                for (int i = 0; i < DPT; i += 4) {
-                    const float4 b4 = *reinterpret_cast<const float4*>(bu + i), c4 = *reinterpret_cast<const float4*>(cu + i);
-                    M[i] = fmaf(dec, M[i], b4.x * xv); M[i + 1] = fmaf(dec, M[i + 1], b4.y * xv);
-                    M[i + 2] = fmaf(dec, M[i + 2], b4.z * xv); M[i + 3] = fmaf(dec, M[i + 3], b4.w * xv);
-                    y = fmaf(M[i], c4.x, fmaf(M[i + 1], c4.y, fmaf(M[i + 2], c4.z, fmaf(M[i + 3], c4.w, y))));
+        for (int u = 0; u < kTok; ++u) {
+            yp[u] = 0.f;
+            if (u < nt) {
+                const float* bu = sb + u * Np + r * DPT;
+                const float* cu = scm + u * Np + r * DPT;
+                const float dec = sc[u * 2], xv = sx[u * kCols + lane];
+                float y = 0.f;
+                if (DPT >= 4) {
+#pragma unroll
+                    for (int i = 0; i < DPT; i += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bu + i), c4 = *reinterpret_cast<const float4*>(cu + i);
+                        M[i] = fmaf(dec, M[i], b4.x * xv); M[i + 1] = fmaf(dec, M[i + 1], b4.y * xv);
+                        M[i + 2] = fmaf(dec, M[i + 2], b4.z * xv); M[i + 3] = fmaf(dec, M[i + 3], b4.w * xv);
+                        y = fmaf(M[i], c4.x, fmaf(M[i + 1], c4.y, fmaf(M[i + 2], c4.z, fmaf(M[i + 3], c4.w, y))));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPT; ++i) { M[i] = fmaf(dec, M[i], bu[i] * xv); y = fmaf(M[i], cu[i], y); }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < DPT; ++i) { M[i] = fmaf(dec, M[i], bu[i] * xv); y = fmaf(M[i], cu[i], y); }
+                yp[u] = y;
             }
-            float* pb = part + ((t0 + u) & 1) * kRowGroups * kCols;
-            pb[r * kCols + lane] = y;
-            __syncthreads();
-            if (r == 0 && col) {
-                y = 0.f;
+        }
 #pragma unroll
-                for (int w = 0; w < kRowGroups; ++w) y += pb[w * kCols + lane];
-                out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(ds, xv, y);
-            }
+        for (int u = 0; u < kTok; ++u) part[(u * kRowGroups + r) * kCols + lane] = yp[u];
+        __syncthreads();
+        if (r < nt && col) {
+            float y = 0.f;
+#pragma unroll
+            for (int w = 0; w < kRowGroups; ++w) y += part[(r * kRowGroups + w) * kCols + lane];
+            out[(((long)b * S + t0 + r) * H + h) * V + j] = fmaf(ds, sx[r * kCols + lane], y);
         }
     }
     if (col) {
@@ -264,7 +273,7 @@ bool ssd_scan(const void* x, long x_sb, long x_st, const void* bm, const void* c
     if (!dpt) return false;
     if (B == 0 || S == 0) return true;
     dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
-    const size_t smem = sizeof(float) * (2 * kTok * dpt * kRowGroups + kTok * kCols + kTok * 2 + 2 * kRowGroups * kCols);
+    const size_t smem = sizeof(float) * (2 * kTok * dpt * kRowGroups + kTok * kCols + kTok * 2 + kTok * kRowGroups * kCols);
 #define SEQMIX_SSD(T, P)                                                                                                              \
     ssd_kernel<T, P><<<grid, block, smem, s>>>((const T*)x, x_sb, x_st, (const T*)bm, (const T*)cm, bc_sb, bc_st, dtraw, dt_sb, dt_st,   \
                                                a_log, dt_bias, dskip, state, slots, lens, fresh, S, H, G, N, V, out)
