@@ -47,7 +47,7 @@ class PiniraxConfig:
     @classmethod
     def from_dict(cls, d: Dict[str, Any], **overrides) -> "PiniraxConfig":
         return cls(vocab=int(d["vocab"]), width=int(d["width"]), layers=list(d["layers"]), norm_eps=float(d["norm"]["eps"]),
-                   embedding_scale=float(d["embedding"]["scale"]), **overrides)
+                   embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), **overrides)
 
     @classmethod
     def from_pretrained(cls, path: str, **overrides) -> "PiniraxConfig":
@@ -64,11 +64,12 @@ def _build_mixer(cfg: PiniraxConfig, spec: Dict[str, Any], max_seq_len: int) -> 
     if kind == "parallel":
         l, r = m["left"], m["right"]
         left = GatedWindowAttention(cfg.width, int(l["heads"]), int(l["kv_heads"]), int(l["dim"]), int(l["vdim"]),
-                                    window=int(l["mask"]["size"]), scale=float(l["scale"]), softcap=float(l["softcap"]),
+                                    window=int(l["mask"]["size"]), scale=float(l.get("scale", int(l["dim"]) ** -0.5)),
+                                    softcap=float(l.get("softcap", 0.0)),
                                     eps=cfg.norm_eps, dtype=cfg.dtype, device=cfg.device, max_seq_len=max_seq_len)
         right = GatedDeltaRule(cfg.width, int(r["heads"]), int(r["kv_heads"]), int(r["dim"]), int(r["vdim"]), int(r["conv"]),
                                eps=cfg.norm_eps, dtype=cfg.dtype, device=cfg.device)
-        return ParallelMixers({"left": left, "right": right}, [float(m["left_scale"]), float(m["right_scale"])])
+        return ParallelMixers({"left": left, "right": right}, [float(m.get("left_scale", 1.0)), float(m.get("right_scale", 1.0))])
     if kind == "mamba2":
         return SelectiveStateSpace(cfg.width, int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["norm_groups"]),
                                    int(m["conv"]), eps=cfg.norm_eps, dtype=cfg.dtype, device=cfg.device)

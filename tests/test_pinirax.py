@@ -198,6 +198,29 @@ def test_short_conv_with_silu_prompt_then_tokens(device, taps, bias):
     assert (torch.cat(got, 1)[0].cpu().double() - want).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("N,E,top,n_real,act", [(7, 12, 4, 8, "softmax"), (40, 5, 5, 5, "softmax"), (3, 70, 9, 64, "softmax"), (9, 33, 2, 30, "sigmoid"), (1, 200, 8, 199, "softmax")])
+def test_router_scores_choice_and_identity_share(device, N, E, top, n_real, act):
+    g = torch.Generator().manual_seed(E)
+    logits, corr = torch.randn(N, E, generator=g) * 2, torch.randn(E, generator=g) * 0.2
+    w, idx, ident = seqmix.route_topk(logits.to(device), corr.to(device), top, n_real, act, 1.5)
+    sc = torch.softmax(logits.double(), -1) if act == "softmax" else torch.sigmoid(logits.double())
+    want = torch.topk(sc + corr.double(), top).indices
+    assert torch.equal(idx.cpu(), want)                                        # descending by corrected score
+    ws = sc.gather(1, want)
+    assert (w.cpu().double() - torch.where(want < n_real, ws * 1.5, 0 * ws)).abs().max() < 1e-6
+    assert (ident.cpu().double() - torch.where(want >= n_real, ws, 0 * ws).sum(1)).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("N,O,I", [(1, 9, 48), (5, 3, 130), (16, 40, 64), (40, 7, 33)])
+def test_float_result_products(device, N, O, I):
+    g = torch.Generator().manual_seed(N * O)
+    big, w = torch.randn(N, I + 6, generator=g), torch.randn(O, I, generator=g)
+    got = seqmix.linear_f32(big.to(device)[:, 3:3 + I], w.to(device)).cpu()
+    assert got.dtype == torch.float32 and (got.double() - big[:, 3:3 + I].double() @ w.double().T).abs().max() < 1e-4
+
+
 def _ffn(f, width, device, seed, dtype=torch.float32):
     cfg = make_cfg([par(mlp=f)], width=width)
     w = random_checkpoint(cfg, seed)
