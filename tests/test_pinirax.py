@@ -165,7 +165,8 @@ def test_embedding_with_sinusoids(device, W):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("rows,C,groups,shared,gate_first", [(7, 48, 4, True, False), (5, 96, 3, False, True), (70, 40, 1, False, True), (3, 66, 2, True, True)])
+@pytest.mark.parametrize("rows,C,groups,shared,gate_first", [(7, 48, 4, True, False), (5, 96, 3, False, True), (70, 40, 1, False, True), (3, 66, 2, True, True),
+                                                             (3, 2048, 1, False, True), (5, 4096, 2, True, False), (2, 1030, 1, False, True)])
 def test_grouped_gated_norm(device, rows, C, groups, shared, gate_first):
     g = torch.Generator().manual_seed(rows)
     x, big = torch.randn(rows, C, generator=g), torch.randn(rows, C + 10, generator=g)
@@ -182,10 +183,10 @@ def test_grouped_gated_norm(device, rows, C, groups, shared, gate_first):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("taps,bias", [(1, False), (2, True), (4, True), (6, False)])
-def test_short_conv_with_silu_prompt_then_tokens(device, taps, bias):
+@pytest.mark.parametrize("taps,bias,C", [(1, False, 44), (2, True, 44), (4, True, 44), (6, False, 44), (3, True, 45), (9, False, 44)])
+def test_short_conv_with_silu_prompt_then_tokens(device, taps, bias, C):
     g = torch.Generator().manual_seed(taps)
-    C, S = 44, 13
+    S = 13
     x, w = torch.randn(1, S, C, generator=g), torch.randn(C, taps, generator=g)
     b = torch.randn(C, generator=g) if bias else None
     want = oracle.silu(oracle.causal_conv(x[0].double(), w.double(), None if b is None else b.double()))
@@ -219,6 +220,27 @@ def test_float_result_products(device, N, O, I):
     big, w = torch.randn(N, I + 6, generator=g), torch.randn(O, I, generator=g)
     got = seqmix.linear_f32(big.to(device)[:, 3:3 + I], w.to(device)).cpu()
     assert got.dtype == torch.float32 and (got.double() - big[:, 3:3 + I].double() @ w.double().T).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("M,F,I", [(5, 7, 50), (40, 64, 48), (3, 33, 131)])
+def test_gated_expert_pieces(device, M, F, I):
+    """``silu(gate) * up`` as an elementwise kernel and inside the expert-streaming product, vector and element-wise layouts; rows
+    that name no expert give zeros."""
+    g = torch.Generator().manual_seed(M * F)
+    gu = torch.randn(M, 2 * F, generator=g)
+    want = oracle.silu(gu[:, :F].double()) * gu[:, F:].double()
+    assert (seqmix.silu_mul(gu.to(device)).cpu().double() - want).abs().max() < 1e-6
+    E = 4
+    w, x = torch.randn(E, 2 * F, I, generator=g) / math.sqrt(I), torch.randn(M, I, generator=g)
+    sel = torch.randint(-1, E + 1, (M,), generator=g).to(torch.int32)
+    got = seqmix.indexed_gemv(w.to(device), sel.to(device), x.to(device), "silu_glu").cpu().double()
+    for m in range(M):
+        if 0 <= int(sel[m]) < E:
+            y = w[int(sel[m])].double() @ x[m].double()
+            assert (got[m] - oracle.silu(y[:F]) * y[F:]).abs().max() < 1e-5
+        else:
+            assert (got[m] == 0).all()
 
 
 def _ffn(f, width, device, seed, dtype=torch.float32):
@@ -298,6 +320,30 @@ def test_window_attention_prompt_and_ring(device, H, G, D, V, window, softcap):
         seqmix.window_attention_token(q1, kc, vc, g1, ctx.slots, ctx.pos0, ctx.lens, window, scale, softcap, o1, 0.8)
         for b in range(B):
             assert (o1[b].cpu().double() - want[b][pos[b]]).abs().max() < 2e-5, (b, t)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,G,D,V,window,ring", [(4, 2, 32, 48, 300, 300), (6, 1, 16, 24, 700, 700), (2, 2, 40, 8, 1000, 260)])
+def test_single_token_attention_over_long_rings(device, H, G, D, V, window, ring):
+    """Rings long enough for the kernel to split them into stretches: positions before the ring is full, at its last row, just
+    after the first wrap and far later, against an explicit sum over the positions the ring rows hold."""
+    g = torch.Generator().manual_seed(ring)
+    pos = [5, ring - 1, ring, 3 * ring + 17] if ring == window else [5, ring - 1, 100, 259]
+    B = len(pos)
+    kc, vc = torch.randn(B + 1, ring, G, D, generator=g), torch.randn(B + 1, ring, G, V, generator=g)
+    q, gate = torch.randn(B, 1, H, D, generator=g), torch.randn(B, 1, H, generator=g)
+    slots, scale, cap = [3, 0, 4, 1], 1.7 / math.sqrt(D), 12.0
+    out = torch.zeros(B, H * V, device=device)
+    ctx = ctx_for([1] * B, slots, pos, False, device)
+    seqmix.window_attention_token(q.to(device), kc.to(device), vc.to(device), gate.to(device), ctx.slots, ctx.pos0, ctx.lens, window, scale, cap, out, 1.0)
+    for b in range(B):
+        js = [j for j in range(max(0, pos[b] - window + 1), pos[b] + 1)]
+        for h in range(H):
+            kk = torch.stack([kc[slots[b], j % ring, h // (H // G)] for j in js]).double()
+            vv = torch.stack([vc[slots[b], j % ring, h // (H // G)] for j in js]).double()
+            sc = cap * torch.tanh((kk @ q[b, 0, h].double()) * scale / cap)
+            want = (torch.softmax(sc, 0)[:, None] * vv).sum(0) * torch.sigmoid(gate[b, 0, h].double())
+            assert (out[b, h * V:(h + 1) * V].cpu().double() - want).abs().max() < 2e-5, (b, h)
 
 
 @pytest.mark.parametrize("device", DEVICES)
